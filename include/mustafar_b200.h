@@ -1,0 +1,157 @@
+/*
+ * mustafar_b200 -- C ABI of the B200 (sm_100a) sparse KV-cache hot path.
+ *
+ * Plain pointers and sizes only; every pointer named "device" must point into
+ * memory reachable from the current CUDA device.  All entry points are
+ * asynchronous on `stream` (a cudaStream_t passed as void*), never allocate
+ * device memory and return an `mfar_status` (0 = ok) for host-side argument
+ * errors or a failed launch.  Device-side problems (capacity overflow, a bounded
+ * wait that gave up) are reported through the optional `dev_status` word.
+ *
+ * Each function names the reference interface (Haozon/mustafar, path inside
+ * that project) it replaces.
+ *
+ * Fixed by the format: head_dim D = 128, a "tile" = 64 logical elements with
+ * one 64-bit bitmap (bit 63-i = element i), a "block" = 64 tokens = 128 tiles.
+ */
+#ifndef MUSTAFAR_B200_H_
+#define MUSTAFAR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MFAR_HEAD_DIM 128
+#define MFAR_TILE 64
+#define MFAR_BLOCK_TOKENS 64
+#define MFAR_TILES_PER_BLOCK 128
+
+typedef enum {
+    MFAR_OK = 0,
+    MFAR_ERR_ARG = 1,          /* bad size / null pointer / unsupported shape     */
+    MFAR_ERR_ALIGN = 2,        /* pointer or stride not aligned as documented     */
+    MFAR_ERR_WORKSPACE = 3,    /* scratch / workspace too small                   */
+    MFAR_ERR_LAUNCH = 4,       /* cudaGetLastError() != success after a launch    */
+    MFAR_ERR_DEVICE = 5,       /* dev_status non-zero (see MFAR_DEV_* bits)       */
+    MFAR_ERR_LIMIT = 6         /* size beyond a fixed limit of the entry point    */
+} mfar_status;
+
+/* bits OR-ed into *dev_status by kernels */
+#define MFAR_DEV_CAPACITY 1u   /* packed values would not fit nz_capacity         */
+#define MFAR_DEV_TIMEOUT 2u    /* a bounded wait gave up (look-back or mbarrier)  */
+#define MFAR_DEV_BADMETA 4u    /* offsets in the cache are inconsistent           */
+
+enum { MFAR_KIND_KEY = 0, MFAR_KIND_VALUE = 1 };
+
+int mfar_version(void);
+const char* mfar_status_string(int status);
+
+/* ------------------------------------------------------------------------- *
+ * Compression: fused per-token magnitude prune + bitmap/packed-value encoding.
+ *
+ * Replaces  kernel/compression.py:249-342  convert_key_batched   (kind = KEY)
+ *           kernel/compression.py:344-435  convert_value_batched (kind = VALUE)
+ *  and, when prune_rank > 0, the pruning in front of them,
+ *           models/llama_mustafar_kernel.py:194-232 / :236-274 (dh_prune_key/value):
+ *           thr = prune_rank-th SMALLEST |x| of the 128 channels of a token,
+ *           keep |x| >= thr (ties kept).  prune_rank = 0: input is taken as is.
+ *
+ * x            device, fp16, element (h, t, c) at x[h*x_head_stride + t*x_token_stride + c];
+ *              strides in elements, multiples of 8; x 16-byte aligned.
+ * n_tokens     multiple of 64.  Tiles are appended at tile index tile_start
+ *              (= tokens already in the cache * 2); tile_start = 0 starts a cache.
+ * bitmaps      device int64, head h at bitmaps + h*bmp_head_stride.
+ * accum        device int32 prefix of padded counts in uint32 units
+ *              (reference `accum_counts`), head h at accum + h*acc_head_stride,
+ *              entry tile_start must already hold the head's current tail when
+ *              tile_start > 0; entry 0 is written as 0 when tile_start == 0.
+ * nz           device fp16 packed values; head h starts at
+ *              nz + 8*nz_offset[h] halves (nz_offset device int32, uint4 units,
+ *              the reference's NZ_Offset) or, when nz_offset is NULL, at
+ *              nz + h*nz_head_stride halves (multiple of 8).
+ * nz_capacity  halves available per head (bounds check; overflow sets
+ *              MFAR_DEV_CAPACITY and the head's remaining blocks are skipped).
+ * scratch      device, mfar_compress_scratch_bytes() bytes, 16-byte aligned;
+ *              cleared by this call (no need to pre-zero).
+ * dev_status   device uint32 or NULL.
+ * max_block_halves  device uint32 or NULL: atomicMax'ed with the packed halves of
+ *              every block written (a safe `stage_halves` for the decode calls).
+ * ------------------------------------------------------------------------- */
+size_t mfar_compress_scratch_bytes(int n_heads, int n_tokens);
+
+int mfar_compress_fp16(const void* x, int64_t x_head_stride, int64_t x_token_stride,
+                       int n_heads, int n_tokens, int kind, int prune_rank,
+                       int64_t* bitmaps, int64_t bmp_head_stride,
+                       int32_t* accum, int64_t acc_head_stride, int64_t tile_start,
+                       void* nz, const int32_t* nz_offset, int64_t nz_head_stride,
+                       int64_t nz_capacity,
+                       void* scratch, size_t scratch_bytes,
+                       uint32_t* dev_status, uint32_t* max_block_halves, void* stream);
+
+/* Prune only (writes x * (|x| >= thr) with the reference's signed zeros).
+ * Replaces models/llama_mustafar_kernel.py:194-232.  In place allowed (y == x). */
+int mfar_prune_fp16(const void* x, void* y, int64_t n_rows, int64_t row_stride,
+                    int prune_rank, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Decode over the fp16 compressed cache.  Common arguments:
+ *
+ * q             device fp16, query of q-head i at q + i*q_stride (128 halves);
+ *               q-head i uses kv head i / group  (kernel/csrc/SpMM_Kernel.cuh:258-265).
+ * n_kv_heads    B * Hkv;  group = Hq / Hkv in {1, 2, 4, 8}.
+ * bitmaps/accum/nz/nz_offset/..._head_stride   the cache as written by
+ *               mfar_compress_fp16 (bmp_head_stride even; bitmaps and nz 16-byte
+ *               aligned); n_tokens = compressed tokens, multiple of 64.
+ * stage_halves  upper bound on the packed halves of any 64-token block of one
+ *               tensor (sizes the shared-memory ring); 0 = worst case 8192.  A
+ *               block larger than the bound sets MFAR_DEV_BADMETA.
+ * ------------------------------------------------------------------------- */
+
+/* Split count and workspace size the decode entry points will use. */
+int mfar_decode_plan(int n_kv_heads, int n_tokens, int window, int nsplit_hint, int* nsplit_out,
+                     size_t* workspace_bytes, int group);
+
+/* Fused decode attention: softmax(q.[K~;Kwin]^T * softmax_scale).[V~;Vwin] for one
+ * query token per q-head, fp32 accumulation, fp16 result out[i*out_stride + c].
+ * Replaces the whole decode-step sequence models/llama_mustafar_kernel.py:394-438
+ * (key op, window matmul, softmax, value op, window matmul, add) in one call.
+ * k_window/v_window: dense fp16 [n_kv_heads][window][128] with the given strides
+ * (elements, multiples of 8); window may be 0.  workspace: mfar_decode_plan bytes. */
+int mfar_decode_attention_fp16(
+    const void* q, int64_t q_stride, int n_kv_heads, int group,
+    const int64_t* k_bitmaps, int64_t k_bmp_head_stride, const int32_t* k_accum, int64_t k_acc_head_stride,
+    const void* k_nz, const int32_t* k_nz_offset, int64_t k_nz_head_stride,
+    const int64_t* v_bitmaps, int64_t v_bmp_head_stride, const int32_t* v_accum, int64_t v_acc_head_stride,
+    const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride,
+    int n_tokens, const void* k_window, const void* v_window, int64_t win_head_stride, int64_t win_token_stride,
+    int window, float softmax_scale, void* out, int64_t out_stride, void* workspace, size_t workspace_bytes,
+    int nsplit, int stage_halves, uint32_t* dev_status, void* stream);
+
+/* scores[i*scores_stride + t] = sum_c K~[i/group][t][c] * q[i][c]  (fp32 accumulate, fp16 store).
+ * Replaces mustafar_key_formulation -> Key_SplitK_API -> Key_Kernel
+ * (kernel/kernel_wrapper/mustafar_wrapper.cu:19-133, kernel/csrc/SpMM_API.cu:179-240,
+ *  kernel/csrc/SpMM_Kernel.cuh:240-520); only row 0 of the reference's 8-row output is real. */
+int mfar_key_scores_fp16(const void* q, int64_t q_stride, int n_kv_heads, int group,
+                         const int64_t* bitmaps, int64_t bmp_head_stride, const int32_t* accum,
+                         int64_t acc_head_stride, const void* nz, const int32_t* nz_offset,
+                         int64_t nz_head_stride, int n_tokens, void* scores, int64_t scores_stride,
+                         int stage_halves, uint32_t* dev_status, void* stream);
+
+/* out[i*out_stride + c] = sum_t V~[i/group][t][c] * probs[i*probs_stride + t].
+ * Replaces mustafar_value_formulation -> Value_SplitK_API -> Value_Kernel (+SplitK_Reduction)
+ * (kernel/kernel_wrapper/mustafar_wrapper.cu:139-263, kernel/csrc/SpMM_API.cu:331-400,
+ *  kernel/csrc/SpMM_Kernel.cuh:535-796, kernel/csrc/Reduction_Kernel.cuh:26-48). */
+int mfar_value_output_fp16(const void* probs, int64_t probs_stride, int n_kv_heads, int group,
+                           const int64_t* bitmaps, int64_t bmp_head_stride, const int32_t* accum,
+                           int64_t acc_head_stride, const void* nz, const int32_t* nz_offset,
+                           int64_t nz_head_stride, int n_tokens, void* out, int64_t out_stride,
+                           void* workspace, size_t workspace_bytes, int nsplit, int stage_halves,
+                           uint32_t* dev_status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MUSTAFAR_B200_H_ */

@@ -1,0 +1,347 @@
+// Fused per-token magnitude prune + bitmap / packed-value compression (fp16 format).
+//
+// One CTA (128 threads) owns one 64-token block of one head: 64 rows x 128 channels.
+//   1. each thread pair loads one 256-byte row straight into registers,
+//   2. finds the rank-th smallest magnitude of the row by a 15-step bisection on the
+//      fp16 bit pattern (packed half2 compares, counts kept in half2, one shuffle
+//      per step to join the pair) and zeroes everything below it,
+//   3. the pruned block goes to shared memory, where one thread per tile builds the
+//      64-bit bitmap (K: one channel down 64 tokens, V: 64 channels of one token),
+//   4. padded counts are scanned inside the CTA; the block's start inside its head
+//      comes from a decoupled look-back over the preceding blocks of the same head,
+//   5. nonzeros are packed in shared memory in final order and leave with 128-bit
+//      coalesced stores.
+// CTAs take (head, block) from an atomic ticket, head-major, so every predecessor a
+// look-back waits for has already started; the wait is bounded all the same.
+#include "common.cuh"
+
+namespace mfar {
+
+constexpr int kXsStride = 144;  // halves per shared-memory row: 288 B keeps 16-B chunks conflict free
+constexpr unsigned long long kFlagAggregate = 1ull << 62;
+constexpr unsigned long long kFlagPrefix = 2ull << 62;
+constexpr unsigned long long kValueMask = (1ull << 62) - 1;
+
+struct CompressParams {
+    const __half* x;
+    int64_t xhs, xts;
+    int n_heads, nblk, rank;
+    unsigned long long* bmp;
+    int64_t bmp_hs;
+    int* acc;
+    int64_t acc_hs, tile_start;
+    __half* nz;
+    const int* nz_off;
+    int64_t nz_hs, nz_cap;
+    unsigned* ticket;              // scratch[0]
+    unsigned* err;                 // scratch[1]
+    unsigned long long* state;     // scratch + 16 bytes: one word per (head, block)
+    unsigned* dev_status;
+    unsigned* max_block;           // optional: running max of packed halves per block
+};
+
+// rank-th smallest magnitude among the 128 values held by a thread pair
+// (m[] = |x| as packed half2, 32 per thread).  Returns the fp16 bit pattern.
+__device__ __forceinline__ unsigned select_threshold(const __half2 (&m)[32], int rank) {
+    unsigned T = 0;
+#pragma unroll 1
+    for (int bit = 14; bit >= 0; --bit) {
+        const unsigned short tr = static_cast<unsigned short>(T | ((1u << bit) - 1u));
+        const __half2 t2 = __half2half2(__ushort_as_half(tr));
+        __half2 c0 = __float2half2_rn(0.f), c1 = c0, c2 = c0, c3 = c0;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+            c0 = __hadd2(c0, __hle2(m[j + 0], t2));
+            c1 = __hadd2(c1, __hle2(m[j + 1], t2));
+            c2 = __hadd2(c2, __hle2(m[j + 2], t2));
+            c3 = __hadd2(c3, __hle2(m[j + 3], t2));
+        }
+        c0 = __hadd2(__hadd2(c0, c1), __hadd2(c2, c3));
+        int cnt = static_cast<int>(__low2float(c0) + __high2float(c0));
+        cnt += __shfl_xor_sync(kFull, cnt, 1);
+        if (cnt < rank) T |= (1u << bit);
+    }
+    return T;
+}
+
+// Loads the pair's half of a row (chunks 2j+hh of 8 halves) and prunes it in registers.
+// keep_sign: leave the sign bit of pruned elements (what x * 0 gives) instead of +0.
+__device__ __forceinline__ void load_prune_row(const __half* row, int hh, int rank, bool keep_sign, uint4 (&v)[8]) {
+    const uint4* src = reinterpret_cast<const uint4*>(row);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = ldg_nc_u4(src + 2 * j + hh);
+    if (rank <= 0) return;
+    __half2 m[32];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const unsigned w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const unsigned a = w[e] & 0x7fff7fffu;
+            m[4 * j + e] = *reinterpret_cast<const __half2*>(&a);
+        }
+    }
+    const unsigned T = select_threshold(m, rank);
+    const __half2 t2 = __half2half2(__ushort_as_half(static_cast<unsigned short>(T)));
+    const unsigned sign = keep_sign ? 0x80008000u : 0u;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        unsigned* w = reinterpret_cast<unsigned*>(&v[j]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) w[e] &= (__hge2_mask(m[4 * j + e], t2) | sign);
+    }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(128) compress_kernel(CompressParams p) {
+    __shared__ __align__(16) unsigned short xs[64 * kXsStride];
+    __shared__ __align__(16) unsigned short ps[64 * 128];
+    __shared__ unsigned s_warp[4];
+    __shared__ unsigned s_ticket;
+    __shared__ long long s_excl;
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) s_ticket = atomicAdd(p.ticket, 1u);
+    __syncthreads();
+    const int h = static_cast<int>(s_ticket) / p.nblk;
+    const int b = static_cast<int>(s_ticket) % p.nblk;
+    if (h >= p.n_heads) return;
+
+    // ---- 1+2: load a row per thread pair, prune in registers, park in shared memory
+    {
+        const int r = tid >> 1, hh = tid & 1;
+        uint4 v[8];
+        load_prune_row(p.x + h * p.xhs + (static_cast<int64_t>(b) * 64 + r) * p.xts, hh, p.rank, false, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(&xs[r * kXsStride + 8 * (2 * j + hh)]) = v[j];
+    }
+    __syncthreads();
+
+    // ---- 3: one thread per tile builds its bitmap
+    unsigned hi = 0, lo = 0;
+    if (KIND == MFAR_KIND_KEY) {
+        const int c = tid;
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i) hi = (hi << 1) | ((xs[i * kXsStride + c] & 0x7fffu) != 0);
+#pragma unroll 8
+        for (int i = 32; i < 64; ++i) lo = (lo << 1) | ((xs[i * kXsStride + c] & 0x7fffu) != 0);
+    } else {
+        const int hf = tid >> 6, i = tid & 63;
+        const unsigned short* row = &xs[i * kXsStride + hf * 64];
+#pragma unroll 8
+        for (int e = 0; e < 32; ++e) hi = (hi << 1) | ((row[e] & 0x7fffu) != 0);
+#pragma unroll 8
+        for (int e = 32; e < 64; ++e) lo = (lo << 1) | ((row[e] & 0x7fffu) != 0);
+    }
+    const unsigned nnz = __popc(hi) + __popc(lo);
+    const unsigned pad = ((nnz + 7u) & ~7u) >> 1;  // uint32 units, reference counts
+
+    // ---- 4a: CTA scan of the 128 padded counts
+    unsigned incl = pad;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const unsigned n = __shfl_up_sync(kFull, incl, d);
+        if (lane >= d) incl += n;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    unsigned wbase = 0, total = 0;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const unsigned t = s_warp[w];
+        if (w < warp) wbase += t;
+        total += t;
+    }
+    incl += wbase;
+    const unsigned excl_tile = incl - pad;
+
+    // ---- 4b: start of this block inside its head (decoupled look-back, warp 0)
+    if (warp == 0) {
+        unsigned long long* st = p.state + static_cast<int64_t>(h) * p.nblk;
+        long long excl = 0;
+        bool failed = false;
+        if (b > 0) {
+            if (lane == 0) st_volatile_u64(st + b, kFlagAggregate | total);
+            int j = b - 1;
+            while (true) {
+                const int idx = j - lane;
+                unsigned long long w = kFlagPrefix;  // virtual predecessor of block 0: prefix 0
+                if (idx >= 0) {
+                    unsigned spins = 0;
+                    while (true) {
+                        w = ld_volatile_u64(st + idx);
+                        if (w >> 62) break;
+                        if (++spins > kSpinLimit || ((spins & 255u) == 0 && ld_volatile_u32(p.err))) {
+                            failed = true;
+                            break;
+                        }
+                        __nanosleep(32);
+                    }
+                }
+                if (__any_sync(kFull, failed)) { failed = true; break; }
+                const unsigned pm = __ballot_sync(kFull, (w >> 62) == 2ull);
+                const int first = pm ? (__ffs(pm) - 1) : 32;
+                const unsigned val = (lane <= first) ? static_cast<unsigned>(w & kValueMask) : 0u;
+                excl += warp_sum_u32(val);
+                if (pm) break;
+                j -= 32;
+            }
+        }
+        if (lane == 0) {
+            if (failed) {
+                atomicOr(p.err, MFAR_DEV_TIMEOUT);
+                if (p.dev_status) atomicOr(p.dev_status, MFAR_DEV_TIMEOUT);
+                s_excl = -1;
+            } else {
+                s_excl = excl;
+            }
+            // publish even after a failure so that successors do not wait for this block
+            st_volatile_u64(st + b, kFlagPrefix | static_cast<unsigned long long>(excl + total));
+        }
+    }
+    __syncthreads();
+    if (s_excl < 0) return;
+
+    const int64_t tile0 = p.tile_start + static_cast<int64_t>(b) * kTilesPerBlock;
+    int* acc = p.acc + h * p.acc_hs;
+    const long long base = (p.tile_start > 0) ? static_cast<long long>(acc[p.tile_start]) : 0ll;
+    const long long blk_start = base + s_excl;  // uint32 units inside the head
+
+    p.bmp[h * p.bmp_hs + tile0 + tid] = (static_cast<unsigned long long>(hi) << 32) | lo;
+    acc[tile0 + tid + 1] = static_cast<int>(blk_start + incl);
+    if (p.tile_start == 0 && b == 0 && tid == 0) acc[0] = 0;
+
+    if (tid == 0 && p.max_block) atomicMax(p.max_block, 2u * total);
+
+    if (2 * (blk_start + total) > p.nz_cap) {
+        if (tid == 0 && p.dev_status) atomicOr(p.dev_status, MFAR_DEV_CAPACITY);
+        return;
+    }
+
+    // ---- 5: pack in shared memory in final order, then stream out
+    {
+        unsigned o = 2 * excl_tile;
+        const unsigned end = 2 * incl;
+        if (KIND == MFAR_KIND_KEY) {
+            const int c = tid;
+#pragma unroll 8
+            for (int i = 0; i < 64; ++i) {
+                const unsigned short u = xs[i * kXsStride + c];
+                if (u & 0x7fffu) ps[o++] = u;
+            }
+        } else {
+            const int hf = tid >> 6, i = tid & 63;
+            const unsigned short* row = &xs[i * kXsStride + hf * 64];
+#pragma unroll 8
+            for (int e = 0; e < 64; ++e) {
+                const unsigned short u = row[e];
+                if (u & 0x7fffu) ps[o++] = u;
+            }
+        }
+        while (o < end) ps[o++] = 0;
+    }
+    __syncthreads();
+    {
+        __half* head_nz = p.nz + (p.nz_off ? 8ll * p.nz_off[h] : h * p.nz_hs);
+        uint4* dst = reinterpret_cast<uint4*>(head_nz + 2 * blk_start);
+        const uint4* src = reinterpret_cast<const uint4*>(ps);
+        const int n16 = static_cast<int>(total >> 2);
+        for (int i = tid; i < n16; i += 128) dst[i] = src[i];
+    }
+}
+
+__global__ void __launch_bounds__(128) prune_kernel(const __half* x, __half* y, int64_t n_rows,
+                                                    int64_t row_stride, int rank) {
+    int64_t pair = (static_cast<int64_t>(blockIdx.x) * 128 + threadIdx.x) >> 1;
+    const int hh = threadIdx.x & 1;
+    // threads past the end redo the last row (no store) so that every warp stays whole for the shuffles
+    const bool valid = pair < n_rows;
+    if (!valid) pair = n_rows - 1;
+    uint4 v[8];
+    load_prune_row(x + pair * row_stride, hh, rank, true, v);
+    if (!valid) return;
+    uint4* dst = reinterpret_cast<uint4*>(y + pair * row_stride);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dst[2 * j + hh] = v[j];
+}
+
+}  // namespace mfar
+
+using namespace mfar;
+
+extern "C" size_t mfar_compress_scratch_bytes(int n_heads, int n_tokens) {
+    if (n_heads <= 0 || n_tokens <= 0) return 16;
+    const size_t nblk = (static_cast<size_t>(n_tokens) + 63) / 64;
+    return 16 + 8 * static_cast<size_t>(n_heads) * nblk;
+}
+
+extern "C" int mfar_compress_fp16(const void* x, int64_t x_head_stride, int64_t x_token_stride,
+                                  int n_heads, int n_tokens, int kind, int prune_rank,
+                                  int64_t* bitmaps, int64_t bmp_head_stride,
+                                  int32_t* accum, int64_t acc_head_stride, int64_t tile_start,
+                                  void* nz, const int32_t* nz_offset, int64_t nz_head_stride,
+                                  int64_t nz_capacity, void* scratch, size_t scratch_bytes,
+                                  uint32_t* dev_status, uint32_t* max_block_halves, void* stream) {
+    if (n_heads < 0 || n_tokens < 0 || (n_tokens % 64) != 0) return MFAR_ERR_ARG;
+    if (kind != MFAR_KIND_KEY && kind != MFAR_KIND_VALUE) return MFAR_ERR_ARG;
+    if (prune_rank < 0 || prune_rank > kD || tile_start < 0 || (tile_start % kTilesPerBlock) != 0) return MFAR_ERR_ARG;
+    if (n_heads == 0 || n_tokens == 0) return MFAR_OK;
+    if (!x || !bitmaps || !accum || !nz || !scratch) return MFAR_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (x_head_stride & 7) || (x_token_stride & 7) ||
+        (reinterpret_cast<uintptr_t>(nz) & 15) || (nz_head_stride & 7) ||
+        (reinterpret_cast<uintptr_t>(scratch) & 15) || (reinterpret_cast<uintptr_t>(bitmaps) & 7) ||
+        (reinterpret_cast<uintptr_t>(accum) & 3))
+        return MFAR_ERR_ALIGN;
+    const size_t need = mfar_compress_scratch_bytes(n_heads, n_tokens);
+    if (scratch_bytes < need) return MFAR_ERR_WORKSPACE;
+    const int nblk = n_tokens / 64;
+    if (static_cast<int64_t>(n_heads) * nblk > 0x7fffffffll) return MFAR_ERR_LIMIT;
+
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (cudaMemsetAsync(scratch, 0, need, s) != cudaSuccess) return MFAR_ERR_LAUNCH;
+
+    CompressParams p;
+    p.x = static_cast<const __half*>(x);
+    p.xhs = x_head_stride;
+    p.xts = x_token_stride;
+    p.n_heads = n_heads;
+    p.nblk = nblk;
+    p.rank = prune_rank;
+    p.bmp = reinterpret_cast<unsigned long long*>(bitmaps);
+    p.bmp_hs = bmp_head_stride;
+    p.acc = accum;
+    p.acc_hs = acc_head_stride;
+    p.tile_start = tile_start;
+    p.nz = static_cast<__half*>(nz);
+    p.nz_off = nz_offset;
+    p.nz_hs = nz_head_stride;
+    p.nz_cap = nz_capacity;
+    p.ticket = static_cast<unsigned*>(scratch);
+    p.err = p.ticket + 1;
+    p.state = reinterpret_cast<unsigned long long*>(static_cast<char*>(scratch) + 16);
+    p.dev_status = dev_status;
+    p.max_block = max_block_halves;
+
+    const unsigned grid = static_cast<unsigned>(n_heads) * static_cast<unsigned>(nblk);
+    if (kind == MFAR_KIND_KEY)
+        compress_kernel<MFAR_KIND_KEY><<<grid, 128, 0, s>>>(p);
+    else
+        compress_kernel<MFAR_KIND_VALUE><<<grid, 128, 0, s>>>(p);
+    return launch_status();
+}
+
+extern "C" int mfar_prune_fp16(const void* x, void* y, int64_t n_rows, int64_t row_stride,
+                               int prune_rank, void* stream) {
+    if (n_rows < 0 || prune_rank < 0 || prune_rank > kD) return MFAR_ERR_ARG;
+    if (n_rows == 0) return MFAR_OK;
+    if (!x || !y) return MFAR_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(y) & 15) || (row_stride & 7))
+        return MFAR_ERR_ALIGN;
+    const int64_t blocks = (n_rows * 2 + 127) / 128;
+    if (blocks > 0x7fffffffll) return MFAR_ERR_LIMIT;
+    prune_kernel<<<static_cast<unsigned>(blocks), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(x), static_cast<__half*>(y), n_rows, row_stride, prune_rank);
+    return launch_status();
+}
