@@ -14,9 +14,15 @@ constexpr int kBlockTokens = MFAR_BLOCK_TOKENS;
 constexpr int kTilesPerBlock = MFAR_TILES_PER_BLOCK;
 constexpr unsigned kFull = 0xffffffffu;
 
-// Upper bound on polls of any flag / mbarrier before a kernel gives up, records
-// MFAR_DEV_TIMEOUT and leaves.  Each poll costs >= ~20 ns, so this is seconds.
-constexpr unsigned kSpinLimit = 1u << 26;
+// Every wait on a flag or an mbarrier is bounded by wall time: after this many
+// nanoseconds the kernel records MFAR_DEV_TIMEOUT and leaves.
+constexpr unsigned long long kWaitLimitNs = 500ull * 1000ull * 1000ull;
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ unsigned lane_id() { return threadIdx.x & 31u; }
 

@@ -170,12 +170,17 @@ __global__ void __launch_bounds__(128) compress_kernel(CompressParams p) {
                 unsigned long long w = kFlagPrefix;  // virtual predecessor of block 0: prefix 0
                 if (idx >= 0) {
                     unsigned spins = 0;
+                    unsigned long long t0 = 0;
                     while (true) {
                         w = ld_volatile_u64(st + idx);
                         if (w >> 62) break;
-                        if (++spins > kSpinLimit || ((spins & 255u) == 0 && ld_volatile_u32(p.err))) {
-                            failed = true;
-                            break;
+                        if ((++spins & 255u) == 0) {
+                            const unsigned long long now = global_timer_ns();
+                            if (t0 == 0) t0 = now;
+                            if (now - t0 > kWaitLimitNs || ld_volatile_u32(p.err)) {
+                                failed = true;
+                                break;
+                            }
                         }
                         __nanosleep(32);
                     }

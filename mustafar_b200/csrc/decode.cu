@@ -262,8 +262,9 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeParams p) {
             if (!mbar_wait(&bars[i % kStages], (i / kStages) & 1)) timed_out = true;
         }
         if (__syncthreads_or(timed_out)) { timed_out = true; break; }   // also publishes the stage hand-off below
-        // the previous block is fully consumed by every warp: its stage may be refilled
-        if (!is_window && tid == 0 && i >= 1 && i - 1 + kStages < nb) issue(i - 1 + kStages);
+        // every warp is done with block i-1, so its stage (untouched so far when i == 0) can
+        // take block i + kStages - 1
+        if (!is_window && tid == 0 && i + kStages - 1 < nb) issue(i + kStages - 1);
 
         // ------------------------------------------------------------ K phase
         if (MODE != MODE_VALUE) {

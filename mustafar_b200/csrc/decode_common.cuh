@@ -31,9 +31,14 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, unsigned 
 }
 // Bounded wait: false when the limit ran out (caller records MFAR_DEV_TIMEOUT and leaves).
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-    for (unsigned i = 0; i < kSpinLimit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    while (true) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    }
 }
 // global -> this CTA's shared memory; src/dst 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, unsigned bytes, unsigned long long* bar) {
