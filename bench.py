@@ -46,6 +46,7 @@ def parse():
     ap.add_argument("--sparsity", type=float, default=0.7)
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--variant", default="auto", choices=["auto", "block", "superblock"])
     return ap.parse_args()
 
 
@@ -231,7 +232,7 @@ def main():
     alg_bytes = algorithmic_bytes(ks, vs, a.window, a.batch)
 
     def step():
-        ops.decode_attention(q, ks, vs, kw, vw, G, out=out, stage_halves=hint)
+        ops.decode_attention(q, ks, vs, kw, vw, G, out=out, stage_halves=hint, variant=a.variant)
 
     def barrier():
         torch.cuda.synchronize()
@@ -261,7 +262,7 @@ def main():
 
     def e2e_step():
         q_dev.copy_(q_host, non_blocking=True)
-        ops.decode_attention(q_dev, ks, vs, kw, vw, G, out=out, stage_halves=hint)
+        ops.decode_attention(q_dev, ks, vs, kw, vw, G, out=out, stage_halves=hint, variant=a.variant)
         out_host.copy_(out, non_blocking=True)
 
     for _ in range(3):

@@ -45,6 +45,7 @@ typedef enum {
 #define MFAR_DEV_BADMETA 4u    /* offsets in the cache are inconsistent           */
 
 enum { MFAR_KIND_KEY = 0, MFAR_KIND_VALUE = 1 };
+enum { MFAR_DECODE_FORCE_BLOCK = 1, MFAR_DECODE_FORCE_SUPERBLOCK = 2 };
 
 int mfar_version(void);
 const char* mfar_status_string(int status);
@@ -119,7 +120,9 @@ int mfar_decode_plan(int n_kv_heads, int n_tokens, int window, int nsplit_hint, 
  * Replaces the whole decode-step sequence models/llama_mustafar_kernel.py:394-438
  * (key op, window matmul, softmax, value op, window matmul, add) in one call.
  * k_window/v_window: dense fp16 [n_kv_heads][window][128] with the given strides
- * (elements, multiples of 8); window may be 0.  workspace: mfar_decode_plan bytes. */
+ * (elements, multiples of 8); window may be 0.  workspace: mfar_decode_plan bytes.
+ * nsplit 0 = automatic.  flags: 0, or one of MFAR_DECODE_FORCE_* to pin the kernel variant
+ * (64-token block kernel / 256-token superblock kernel) instead of the size heuristic. */
 int mfar_decode_attention_fp16(
     const void* q, int64_t q_stride, int n_kv_heads, int group,
     const int64_t* k_bitmaps, int64_t k_bmp_head_stride, const int32_t* k_accum, int64_t k_acc_head_stride,
@@ -128,7 +131,7 @@ int mfar_decode_attention_fp16(
     const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride,
     int n_tokens, const void* k_window, const void* v_window, int64_t win_head_stride, int64_t win_token_stride,
     int window, float softmax_scale, void* out, int64_t out_stride, void* workspace, size_t workspace_bytes,
-    int nsplit, int stage_halves, uint32_t* dev_status, void* stream);
+    int nsplit, int stage_halves, int flags, uint32_t* dev_status, void* stream);
 
 /* scores[i*scores_stride + t] = sum_c K~[i/group][t][c] * q[i][c]  (fp32 accumulate, fp16 store).
  * Replaces mustafar_key_formulation -> Key_SplitK_API -> Key_Kernel

@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmustafar_b200.so")
+# MUSTAFAR_B200_LIB points at an alternative build of the same ABI (kernel experiments)
+LIB_PATH = os.environ.get("MUSTAFAR_B200_LIB") or os.path.join(_HERE, "libmustafar_b200.so")
 
 OK = 0
 DEV_CAPACITY, DEV_TIMEOUT, DEV_BADMETA = 1, 2, 4
@@ -29,7 +30,7 @@ SIGNATURES = {
                                           _vp, _i64, _vp, _i64, _vp, _vp, _i64,
                                           _vp, _i64, _vp, _i64, _vp, _vp, _i64,
                                           _i32, _vp, _vp, _i64, _i64, _i32, _f32, _vp, _i64, _vp, _sz,
-                                          _i32, _i32, _vp, _vp]),
+                                          _i32, _i32, _i32, _vp, _vp]),
     "mfar_key_scores_fp16": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32,
                                     _vp, _i64, _i32, _vp, _vp]),
     "mfar_value_output_fp16": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32,

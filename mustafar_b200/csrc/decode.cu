@@ -9,8 +9,8 @@
 // A CTA (4 warps) walks a range of 64-token blocks of ONE kv head and serves all G
 // query heads that share it, so the compressed bytes are read once.  Per block the
 // two bitmap arrays (1 KiB each) and the two packed-value ranges are brought into a
-// 3-stage shared-memory ring by 1-D bulk copies (cp.async.bulk + mbarrier, issued by
-// one thread two blocks ahead).  Tiles are decoded straight from the bitmap:
+// 2-stage shared-memory ring by 1-D bulk copies (cp.async.bulk + mbarrier, issued by
+// one thread one block ahead; four CTAs per SM keep ~60 KB in flight).  Tiles are decoded straight from the bitmap:
 //   * a lane owns one BYTE of a tile's bitmap = 8 consecutive positions, 8 lanes
 //     cover a tile, a warp does 4 tiles per step;
 //   * rank of the lane's first position = popc of the bitmap bits before its byte;
@@ -23,41 +23,14 @@
 
 namespace mfar {
 
-enum { MODE_ATTN = 0, MODE_KEY = 1, MODE_VALUE = 2 };
-
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
-constexpr int kStages = 3;
+#ifndef MFAR_STAGES
+#define MFAR_STAGES 2
+#endif
+constexpr int kStages = MFAR_STAGES;
 constexpr int kPlanes = kWarps * 4;          // K-phase partial planes: (warp, lane group)
 constexpr int kMaxBlocksPerSplit = 256;
-constexpr int kSlackHalves = 64;             // a decode never reads further than this past a stage's values
-
-struct Sparse {
-    const unsigned long long* bmp;
-    const int* acc;
-    const __half* nz;
-    const int* nz_off;
-    int64_t bmp_hs, acc_hs, nz_hs;
-};
-
-struct DecodeParams {
-    Sparse k, v;
-    const __half* q;       // [Bq][q_stride]
-    int64_t q_stride;
-    const __half* kwin;    // dense window [Bh][W][128]
-    const __half* vwin;
-    int64_t win_hs, win_ts;
-    int W;
-    int nblk, nsplit, bps; // compressed blocks, splits over them, blocks per split
-    int cap;               // halves of packed values a stage can hold per tensor
-    float scale_log2;      // softmax scale * log2(e)
-    float* ws;             // split partials
-    __half* s_out;         // MODE_KEY  : [Bq][s_stride]
-    int64_t s_stride;
-    const __half* p_in;    // MODE_VALUE: [Bq][p_stride]
-    int64_t p_stride;
-    unsigned* dev_status;
-};
 
 // A stage holds, per staged tensor, 1 KiB of bitmaps and cap (+slack) packed halves;
 // ATTN stages both K and V, KEY / VALUE only their own.
@@ -90,43 +63,17 @@ struct SmemLayout {
     }
 };
 
-// One tile step for one lane: `hi:lo` is the tile's bitmap, `vals` its packed values,
-// the lane owns byte (positions 8k..8k+7); sel/mh/ml are the lane's constants.
-template <int G>
-__device__ __forceinline__ void tile_step(unsigned hi, unsigned lo, const unsigned short* vals, unsigned sel,
-                                          unsigned mh, unsigned ml, const float (&coef)[G], float (&acc)[8][G]) {
-    const unsigned byte = __byte_perm(lo, hi, sel);
-    const unsigned short* pv = vals + (__popc(hi & mh) + __popc(lo & ml));
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const bool on = (byte & (0x80u >> i)) != 0;
-        unsigned short u = 0;
-        if (on) u = *pv;
-        pv += on;
-        const float v = __half2float(__ushort_as_half(u));
-#pragma unroll
-        for (int g = 0; g < G; ++g) acc[i][g] = fmaf(v, coef[g], acc[i][g]);
-    }
-}
-
-template <int G>
-__device__ __forceinline__ void load_coef(const float* p, float (&c)[G]) {
-    if constexpr (G == 1) {
-        c[0] = p[0];
-    } else if constexpr (G == 2) {
-        const float2 t = *reinterpret_cast<const float2*>(p);
-        c[0] = t.x; c[1] = t.y;
-    } else {
-#pragma unroll
-        for (int g = 0; g < G; g += 4) {
-            const float4 t = *reinterpret_cast<const float4*>(p + g);
-            c[g] = t.x; c[g + 1] = t.y; c[g + 2] = t.z; c[g + 3] = t.w;
-        }
-    }
-}
+#ifndef MFAR_MIN_BLOCKS
+#define MFAR_MIN_BLOCKS 4
+#endif
+#ifndef MFAR_STEP_UNROLL
+#define MFAR_STEP_UNROLL 8
+#endif
+#define MFAR_PRAGMA(x) _Pragma(#x)
+#define MFAR_UNROLL(n) MFAR_PRAGMA(unroll n)
 
 template <int G, int MODE>
-__global__ void __launch_bounds__(kThreads) decode_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(kThreads, MFAR_MIN_BLOCKS) decode_kernel(DecodeParams p) {
     extern __shared__ __align__(128) unsigned char smem[];
     const SmemLayout<G, MODE> lay(p.cap);
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + lay.bars);
@@ -141,13 +88,11 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeParams p) {
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int h = blockIdx.y;
-    const int split = blockIdx.x;
+    const int split = blockIdx.x + p.split_offset;
     const bool is_window = (MODE == MODE_ATTN) && (split == p.nsplit);
     const int gi = lane >> 3, kb = lane & 7;
-    // lane constants of the byte decode
-    const unsigned sel = 7u - kb;
-    const unsigned mh = kb == 0 ? 0u : (kb >= 4 ? 0xffffffffu : (0xffffffffu << (32 - 8 * kb)));
-    const unsigned ml = kb <= 4 ? 0u : (0xffffffffu << (64 - 8 * kb));
+    unsigned sel, mh, ml;
+    lane_byte_constants(kb, sel, mh, ml);
 
     const int blk0 = is_window ? 0 : split * p.bps;
     int nb = is_window ? (p.W + 63) / 64 : min(p.bps, p.nblk - blk0);
@@ -274,7 +219,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeParams p) {
 #pragma unroll
                 for (int g = 0; g < G; ++g) acc_s[t][g] = 0.f;
             if (!is_window) {
-#pragma unroll 2
+MFAR_UNROLL(MFAR_STEP_UNROLL)
                 for (int s = 0; s < 32 / 4; ++s) {
                     const int c = warp * 32 + s * 4 + gi;
                     const uint2 bm = kbm[c];
@@ -380,7 +325,7 @@ __global__ void __launch_bounds__(kThreads) decode_kernel(DecodeParams p) {
             }
             const int half_id = gi & 1, par = gi >> 1;
             if (!is_window) {
-#pragma unroll 2
+MFAR_UNROLL(MFAR_STEP_UNROLL)
                 for (int s = 0; s < 16 / 2; ++s) {
                     const int t = warp * 16 + s * 2 + par;
                     const int tile = half_id * 64 + t;
@@ -531,31 +476,48 @@ static int check_sparse(const void* bmp, const void* acc, const void* nz, int64_
 
 using namespace mfar;
 
+// superblock path: splits in units of 4 blocks, ~8 CTAs per SM over the whole grid
+static void sb_split(int n_kv_heads, int nblk, int hint, int* ns_out, int* sps_out) {
+    const int nsb = (nblk + 3) / 4;
+    int ns = hint > 0 ? hint : (148 * 8 + n_kv_heads - 1) / n_kv_heads;
+    if (ns > nsb) ns = nsb;
+    if (ns < 1) ns = 1;
+    int sps = (nsb + ns - 1) / ns;
+    if (sps * 4 > 1024) sps = 256;
+    *sps_out = sps;
+    *ns_out = (nsb + sps - 1) / sps;
+}
+
+static int block_split(int n_kv_heads, int nblk, int hint) {
+    if (nblk <= 0) return 0;
+    const int min_ns = (nblk + kMaxBlocksPerSplit - 1) / kMaxBlocksPerSplit;
+    int ns;
+    if (hint > 0) {
+        ns = hint;
+    } else {
+        // ~4 CTAs per SM over 148 SMs, at least 2 blocks per split
+        ns = (148 * 4 + n_kv_heads - 1) / n_kv_heads;
+        const int max_ns = (nblk + 1) / 2;
+        if (ns > max_ns) ns = max_ns;
+    }
+    if (ns < min_ns) ns = min_ns;
+    if (ns > nblk) ns = nblk;
+    if (ns < 1) ns = 1;
+    const int bps = (nblk + ns - 1) / ns;
+    return (nblk + bps - 1) / bps;   // no empty splits
+}
+
 extern "C" int mfar_decode_plan(int n_kv_heads, int n_tokens, int window, int nsplit_hint, int* nsplit_out,
                                 size_t* workspace_bytes, int group) {
     if (n_kv_heads <= 0 || n_tokens < 0 || (n_tokens % 64) || window < 0 || group <= 0) return MFAR_ERR_ARG;
     const int nblk = n_tokens / 64;
-    int ns = 0;
-    if (nblk > 0) {
-        const int min_ns = (nblk + kMaxBlocksPerSplit - 1) / kMaxBlocksPerSplit;
-        if (nsplit_hint > 0) {
-            ns = nsplit_hint;
-        } else {
-            // aim for ~4 CTAs per SM slot pair over 148 SMs, at least 2 blocks per split
-            const int target = 148 * 4;
-            ns = (target + n_kv_heads - 1) / n_kv_heads;
-            const int max_ns = (nblk + 1) / 2;
-            if (ns > max_ns) ns = max_ns;
-        }
-        if (ns < min_ns) ns = min_ns;
-        if (ns > nblk) ns = nblk;
-        if (ns < 1) ns = 1;
-        const int bps = (nblk + ns - 1) / ns;
-        ns = (nblk + bps - 1) / bps;   // no empty splits
-    }
+    const int ns = block_split(n_kv_heads, nblk, nsplit_hint);
+    int ns_sb = 0, sps = 0;
+    if (nblk > 0) sb_split(n_kv_heads, nblk, nsplit_hint, &ns_sb, &sps);
+    const int recs = (ns > ns_sb ? ns : ns_sb) + 1;
     if (nsplit_out) *nsplit_out = ns;
     if (workspace_bytes)
-        *workspace_bytes = static_cast<size_t>(n_kv_heads) * (ns + 1) * group * kPartialStride * sizeof(float) + 16;
+        *workspace_bytes = static_cast<size_t>(n_kv_heads) * recs * group * kPartialStride * sizeof(float) + 16;
     return MFAR_OK;
 }
 
@@ -567,9 +529,10 @@ extern "C" int mfar_decode_attention_fp16(
     const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride,
     int n_tokens, const void* k_window, const void* v_window, int64_t win_head_stride, int64_t win_token_stride,
     int window, float softmax_scale, void* out, int64_t out_stride, void* workspace, size_t workspace_bytes,
-    int nsplit, int stage_halves, uint32_t* dev_status, void* stream) {
+    int nsplit, int stage_halves, int flags, uint32_t* dev_status, void* stream) {
     if (n_kv_heads <= 0 || group <= 0 || n_tokens < 0 || (n_tokens % 64) || window < 0) return MFAR_ERR_ARG;
     if (n_tokens == 0 && window == 0) return MFAR_ERR_ARG;
+    if (group != 1 && group != 2 && group != 4 && group != 8) return MFAR_ERR_ARG;
     if (!q || !out || !workspace) return MFAR_ERR_ARG;
     if (window > 0 && (!k_window || !v_window)) return MFAR_ERR_ARG;
     if (window > 0 && ((reinterpret_cast<uintptr_t>(k_window) & 15) || (reinterpret_cast<uintptr_t>(v_window) & 15) ||
@@ -600,17 +563,44 @@ extern "C" int mfar_decode_attention_fp16(
     p.win_ts = win_token_stride;
     p.W = window;
     p.nblk = n_tokens / 64;
-    p.nsplit = ns;
-    p.bps = ns > 0 ? (p.nblk + ns - 1) / ns : 0;
     p.cap = pick_cap(stage_halves);
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.ws = static_cast<float*>(workspace);
     p.dev_status = dev_status;
-
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const int nrec = ns + (window > 0 ? 1 : 0);
-    r = dispatch_decode<MODE_ATTN>(p, group, n_kv_heads, nrec, s);
-    if (r) return r;
+
+    // Two kernels: the 64-token block kernel (4 CTAs per SM) and the 256-token superblock kernel
+    // (one fat CTA per SM, fewer barriers).
+    const int nsb = (p.nblk + 3) / 4;
+    // Measured on B200 (batch 64, 32768 tokens, group 4): block kernel 2.03 ms, superblock kernel
+    // 2.55 ms, so the size heuristic currently always picks the block kernel.
+    bool use_sb = false;
+    (void)nsb;
+    if ((flags & MFAR_DECODE_FORCE_SUPERBLOCK) && p.nblk > 0 && decode_sb_fits(p.cap, group)) use_sb = true;
+
+    int nrec;
+    if (use_sb) {
+        int sps = 0;
+        sb_split(n_kv_heads, p.nblk, nsplit, &ns, &sps);
+        p.nsplit = ns;
+        p.bps = sps;
+        nrec = ns + (window > 0 ? 1 : 0);
+        r = launch_decode_sb(p, group, n_kv_heads, s);
+        if (r) return r;
+        if (window > 0) {   // the dense window is one more record, written by the block kernel
+            DecodeParams pw = p;
+            pw.split_offset = ns;
+            pw.cap = 8;
+            r = dispatch_decode<MODE_ATTN>(pw, group, n_kv_heads, 1, s);
+            if (r) return r;
+        }
+    } else {
+        p.nsplit = ns;
+        p.bps = ns > 0 ? (p.nblk + ns - 1) / ns : 0;
+        nrec = ns + (window > 0 ? 1 : 0);
+        r = dispatch_decode<MODE_ATTN>(p, group, n_kv_heads, nrec, s);
+        if (r) return r;
+    }
     combine_kernel<<<n_kv_heads * group, 128, 0, s>>>(p.ws, nrec, group, 1, static_cast<__half*>(out), out_stride);
     return launch_status();
 }

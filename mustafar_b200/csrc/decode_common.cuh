@@ -65,10 +65,102 @@ __device__ __forceinline__ float warp_sum_f32(float v) {
     return v;
 }
 
+// One tile step for one lane.  `hi:lo` is the tile's 64-bit bitmap (bit 63-i = element i),
+// `vals` its packed values in shared memory.  The lane owns byte `kb` of the bitmap, i.e.
+// positions 8*kb .. 8*kb+7: sel / mh / ml are the lane constants that extract that byte and
+// mask the bits in front of it.  The rank of the lane's first position is the popcount of
+// the bits before its byte; every set bit then consumes the next packed half and is
+// multiply-accumulated in fp32 into acc[i][g] with the per-tile coefficients coef[g]
+// (K phase: the query channel; V phase: the probability of the token).  The compiler turns
+// the `if` into predicated instructions (no branch, no zero fill).
+#ifndef MFAR_CHAINS
+#define MFAR_CHAINS 1
+#endif
+template <int G>
+__device__ __forceinline__ void tile_step(unsigned hi, unsigned lo, const unsigned short* vals, unsigned sel,
+                                          unsigned mh, unsigned ml, const float (&coef)[G], float (&acc)[8][G]) {
+    const unsigned byte = __byte_perm(lo, hi, sel);
+    // MFAR_CHAINS independent read pointers (each covers 8 / MFAR_CHAINS positions) keep the
+    // dependent chain of pointer bumps short
+    const unsigned short* pv[MFAR_CHAINS];
+    pv[0] = vals + (__popc(hi & mh) + __popc(lo & ml));
+#pragma unroll
+    for (int c = 1; c < MFAR_CHAINS; ++c)
+        pv[c] = pv[0] + __popc(byte & (0xffu & ~(0xffu >> (c * (8 / MFAR_CHAINS)))));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const unsigned short*& p = pv[i / (8 / MFAR_CHAINS)];
+        if (byte & (0x80u >> i)) {
+            const float v = __half2float(__ushort_as_half(*p));
+            ++p;
+#pragma unroll
+            for (int g = 0; g < G; ++g) acc[i][g] = fmaf(v, coef[g], acc[i][g]);
+        }
+    }
+}
+
+__device__ __forceinline__ void lane_byte_constants(int kb, unsigned& sel, unsigned& mh, unsigned& ml) {
+    sel = 7u - kb;
+    mh = kb == 0 ? 0u : (kb >= 4 ? 0xffffffffu : (0xffffffffu << (32 - 8 * kb)));
+    ml = kb <= 4 ? 0u : (0xffffffffu << (64 - 8 * kb));
+}
+
+template <int G>
+__device__ __forceinline__ void load_coef(const float* p, float (&c)[G]) {
+    if constexpr (G == 1) {
+        c[0] = p[0];
+    } else if constexpr (G == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(p);
+        c[0] = t.x; c[1] = t.y;
+    } else {
+#pragma unroll
+        for (int g = 0; g < G; g += 4) {
+            const float4 t = *reinterpret_cast<const float4*>(p + g);
+            c[g] = t.x; c[g + 1] = t.y; c[g + 2] = t.z; c[g + 3] = t.w;
+        }
+    }
+}
+
 // Split-KV partial of one (kv head, split, q head of the group): 128 un-normalised
 // output channels, then the running max (log2 domain) and the running sum.
 constexpr int kPartialStride = kD + 4;  // floats; keeps records 16-byte aligned
 constexpr int kPartM = kD;
 constexpr int kPartL = kD + 1;
+
+enum { MODE_ATTN = 0, MODE_KEY = 1, MODE_VALUE = 2 };
+constexpr int kSlackHalves = 64;  // a decode never reads further than this past a stage's values
+
+struct Sparse {
+    const unsigned long long* bmp;
+    const int* acc;
+    const __half* nz;
+    const int* nz_off;
+    int64_t bmp_hs, acc_hs, nz_hs;
+};
+
+struct DecodeParams {
+    Sparse k, v;
+    const __half* q;       // [Bq][q_stride]
+    int64_t q_stride;
+    const __half* kwin;    // dense window [Bh][W][128]
+    const __half* vwin;
+    int64_t win_hs, win_ts;
+    int W;
+    int nblk, nsplit, bps; // compressed blocks, splits over them, blocks per split
+    int cap;               // halves of packed values a stage can hold per tensor
+    float scale_log2;      // softmax scale * log2(e)
+    float* ws;             // split partials
+    __half* s_out;         // MODE_KEY  : [Bq][s_stride]
+    int64_t s_stride;
+    const __half* p_in;    // MODE_VALUE: [Bq][p_stride]
+    int64_t p_stride;
+    unsigned* dev_status;
+    int split_offset;      // added to blockIdx.x (lets a launch cover only the window record)
+};
+
+
+// 64-token-block kernel (decode.cu) and 256-token-superblock kernel (decode_sb.cu)
+int launch_decode_sb(const DecodeParams& p, int G, int n_kv_heads, cudaStream_t s);
+bool decode_sb_fits(int cap, int G);
 
 }  // namespace mfar

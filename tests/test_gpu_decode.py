@@ -91,7 +91,8 @@ def test_value_formulation(m, G, Bh, L):
     (4, 2, 0, 200, 0.7),          # nothing compressed yet
     (1, 2, 64, 0, 0.0),           # unpruned: every tile full, worst-case stage
 ])
-def test_fused_decode_attention(m, G, Bh, L, W, s):
+@pytest.mark.parametrize("variant", ["block", "superblock"])
+def test_fused_decode_attention(m, G, Bh, L, W, s, variant):
     if s > 0:
         kp, vp, ks, vs = build_cache(m, Bh, L, s, 31 + L + W)
     else:
@@ -103,7 +104,8 @@ def test_fused_decode_attention(m, G, Bh, L, W, s):
     kw, vw = kw[:, :W], vw[:, :W]
     q = oracle.make_query(Bh * G, seed=8 + L)
     want = oracle.decode_attention_ref(q, kp, vp, kw, vw, G)
-    out = m.o.decode_attention(q.cuda(), ks, vs, kw.cuda() if W else None, vw.cuda() if W else None, G)
+    out = m.o.decode_attention(q.cuda(), ks, vs, kw.cuda() if W else None, vw.cuda() if W else None, G,
+                               variant=variant)
     assert oracle.rel_l2(out.float().cpu(), want) < TOL
     if L and W:
         # the reference's own order of fp16 roundings agrees to the same tolerance
@@ -111,11 +113,15 @@ def test_fused_decode_attention(m, G, Bh, L, W, s):
         assert oracle.rel_l2(out.float().cpu(), model.float()) < 2 * TOL
 
 
-def test_decode_split_invariance(m):
-    kp, vp, ks, vs = build_cache(m, 2, 2048, 0.7, 5)
+@pytest.mark.parametrize("variant", ["block", "superblock"])
+def test_decode_split_invariance(m, variant):
+    kp, vp, ks, vs = build_cache(m, 2, 2048 + 64, 0.7, 5)     # 33 blocks: ragged last superblock
     kw, vw = oracle.make_kv(2, 128, seed=6)
     q = oracle.make_query(8, seed=7).cuda()
-    outs = [m.o.decode_attention(q, ks, vs, kw.cuda(), vw.cuda(), 4, nsplit=n).float() for n in (1, 3, 32)]
+    outs = [m.o.decode_attention(q, ks, vs, kw.cuda(), vw.cuda(), 4, nsplit=n, variant=variant).float()
+            for n in (1, 3, 32)]
+    want = oracle.decode_attention_ref(q.cpu(), kp, vp, kw, vw, 4)
+    assert oracle.rel_l2(outs[0].cpu(), want) < TOL
     for o in outs[1:]:
         assert oracle.rel_l2(o.cpu(), outs[0].cpu()) < 1e-3
 
