@@ -98,6 +98,35 @@ int mfar_prune_fp16(const void* x, void* y, int64_t n_rows, int64_t row_stride,
                     int prune_rank, void* stream);
 
 /* ------------------------------------------------------------------------- *
+ * Quantised compression: prune + bitmap + per-group asymmetric `bits`-bit codes.
+ *
+ * Replaces  kernel_quant/compression_quant.py:159-264  convert_key_batched_quant   (kind = KEY)
+ *           kernel_quant/compression_quant.py:425-529  convert_value_batched_quant (kind = VALUE)
+ * with bits = 2, group = 64 (bit-exact: scale = (max-min)/3 and zero = floor(-min/scale+0.5) in
+ * fp32, stored fp16; codes from the stored fp16 parameters with IEEE division).  bits = 4 and
+ * group = 32 (a fresh scale/zero every 32 nonzeros of a tile) have no reference counterpart.
+ *
+ * x, strides, n_tokens, kind, prune_rank, bitmaps, tile_start: as mfar_compress_fp16.
+ * tile_offsets/counts/units  device int32, head h at + h*meta_head_stride (counts, units may be NULL);
+ *              tile_offsets[t] = uint32 offset of tile t in the flat `packed` buffer.
+ * scales/zeros device fp16, (64/group) entries per tile: index (h*meta_head_stride + t)*(64/group) + g.
+ * packed       device uint32 codes, 32/bits per word, least significant first.
+ *   packed_head_stride == 0 : compact, heads back to back from offset 0 (the reference's
+ *              layout); packed_capacity = words available in total; head_tail (NULL or device
+ *              int32[n_heads]) receives the end offset of every head.
+ *   packed_head_stride  > 0 : arena, head h owns [h*stride, h*stride + packed_capacity);
+ *              head_tail[h] (required) = words already used, updated by the call.
+ * scratch      mfar_compress_scratch_bytes() bytes, cleared by the call.
+ * ------------------------------------------------------------------------- */
+int mfar_compress_quant(const void* x, int64_t x_head_stride, int64_t x_token_stride, int n_heads,
+                        int n_tokens, int kind, int prune_rank, int bits, int group,
+                        int64_t* bitmaps, int64_t bmp_head_stride, int32_t* tile_offsets,
+                        int32_t* counts, int32_t* units, void* scales, void* zeros,
+                        int64_t meta_head_stride, int64_t tile_start, int32_t* packed,
+                        int64_t packed_head_stride, int64_t packed_capacity, int32_t* head_tail,
+                        void* scratch, size_t scratch_bytes, uint32_t* dev_status, void* stream);
+
+/* ------------------------------------------------------------------------- *
  * Decode over the fp16 compressed cache.  Common arguments:
  *
  * q             device fp16, query of q-head i at q + i*q_stride (128 halves);
@@ -153,6 +182,46 @@ int mfar_value_output_fp16(const void* probs, int64_t probs_stride, int n_kv_hea
                            int64_t nz_head_stride, int n_tokens, void* out, int64_t out_stride,
                            void* workspace, size_t workspace_bytes, int nsplit, int stage_halves,
                            uint32_t* dev_status, void* stream);
+
+/* ------------------------------------------------------------------------- *
+ * Decode over the quantised cache written by mfar_compress_quant (bits in {2,4},
+ * qgroup in {64, 32}); dequantisation fp16((code - zero) * scale) is fused into the SpMV.
+ * Arguments as their fp16 counterparts; tile_offsets / scales / zeros share
+ * meta_head_stride (tiles per head), packed_words bounds every access to `packed`.
+ * ------------------------------------------------------------------------- */
+
+/* Replaces mustafar_key_formulation_quant[_meta] -> Key_SplitK_API_Quant -> Key_Kernel_Quant
+ * (kernel_quant/kernel_wrapper/mustafar_wrapper_quant.cu:14-215, kernel_quant/csrc/SpMM_API_Quant.cu:263-340,
+ *  kernel_quant/csrc/SpMM_Kernel_Quant.cuh:273-503). */
+int mfar_key_scores_quant(const void* q, int64_t q_stride, int n_kv_heads, int group,
+                          const int64_t* bitmaps, int64_t bmp_head_stride, const int32_t* tile_offsets,
+                          const void* scales, const void* zeros, int64_t meta_head_stride,
+                          const int32_t* packed, int64_t packed_words, int n_tokens, int bits, int qgroup,
+                          void* scores, int64_t scores_stride, uint32_t* dev_status, void* stream);
+
+/* Replaces mustafar_value_formulation_quant and ..._decode_n1 -> Value_SplitK_API_Quant -> Value_Kernel_Quant
+ * (kernel_quant/kernel_wrapper/mustafar_wrapper_quant.cu:217-457, kernel_quant/csrc/SpMM_API_Quant.cu:342-573,
+ *  kernel_quant/csrc/SpMM_Kernel_Quant.cuh:510-735).  workspace: n_kv_heads * splits * group * 132 floats,
+ *  splits <= max(1, n_tokens / 128) unless nsplit is given. */
+int mfar_value_output_quant(const void* probs, int64_t probs_stride, int n_kv_heads, int group,
+                            const int64_t* bitmaps, int64_t bmp_head_stride, const int32_t* tile_offsets,
+                            const void* scales, const void* zeros, int64_t meta_head_stride,
+                            const int32_t* packed, int64_t packed_words, int n_tokens, int bits, int qgroup,
+                            void* out, int64_t out_stride, void* workspace, size_t workspace_bytes,
+                            int nsplit, uint32_t* dev_status, void* stream);
+
+/* Fused decode attention over the quantised cache + dense fp16 window (the quantised model's decode step,
+ * models/llama_mustafar_quant_kernel.py:426-662, in one call).  workspace as mfar_decode_plan. */
+int mfar_decode_attention_quant(
+    const void* q, int64_t q_stride, int n_kv_heads, int group,
+    const int64_t* k_bitmaps, const int32_t* k_tile_offsets, const void* k_scales, const void* k_zeros,
+    const int32_t* k_packed, int64_t k_packed_words,
+    const int64_t* v_bitmaps, const int32_t* v_tile_offsets, const void* v_scales, const void* v_zeros,
+    const int32_t* v_packed, int64_t v_packed_words,
+    int64_t bmp_head_stride, int64_t meta_head_stride, int n_tokens, int bits, int qgroup,
+    const void* k_window, const void* v_window, int64_t win_head_stride, int64_t win_token_stride, int window,
+    float softmax_scale, void* out, int64_t out_stride, void* workspace, size_t workspace_bytes, int nsplit,
+    uint32_t* dev_status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -25,6 +25,8 @@ SIGNATURES = {
     "mfar_compress_fp16": (_i32, [_vp, _i64, _i64, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _i64,
                                   _vp, _vp, _i64, _i64, _vp, _sz, _vp, _vp, _vp]),
     "mfar_prune_fp16": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),
+    "mfar_compress_quant": (_i32, [_vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp,
+                                   _i64, _i64, _vp, _i64, _i64, _vp, _vp, _sz, _vp, _vp]),
     "mfar_decode_plan": (_i32, [_i32, _i32, _i32, _i32, C.POINTER(_i32), C.POINTER(_sz), _i32]),
     "mfar_decode_attention_fp16": (_i32, [_vp, _i64, _i32, _i32,
                                           _vp, _i64, _vp, _i64, _vp, _vp, _i64,
@@ -35,6 +37,16 @@ SIGNATURES = {
                                     _vp, _i64, _i32, _vp, _vp]),
     "mfar_value_output_fp16": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32,
                                       _vp, _i64, _vp, _sz, _i32, _i32, _vp, _vp]),
+    "mfar_key_scores_quant": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _i32, _i32, _i32,
+                                     _vp, _i64, _vp, _vp]),
+    "mfar_value_output_quant": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _i32, _i32, _i32,
+                                       _vp, _i64, _vp, _sz, _i32, _vp, _vp]),
+    "mfar_decode_attention_quant": (_i32, [_vp, _i64, _i32, _i32,
+                                           _vp, _vp, _vp, _vp, _vp, _i64,
+                                           _vp, _vp, _vp, _vp, _vp, _i64,
+                                           _i64, _i64, _i32, _i32, _i32,
+                                           _vp, _vp, _i64, _i64, _i32,
+                                           _f32, _vp, _i64, _vp, _sz, _i32, _vp, _vp]),
 }
 
 _lib = None

@@ -472,6 +472,35 @@ static int check_sparse(const void* bmp, const void* acc, const void* nz, int64_
     return MFAR_OK;
 }
 
+int launch_combine(const float* ws, int nrec, int G, int normalise, void* out, int64_t out_stride, int n_q_heads,
+                   cudaStream_t s) {
+    combine_kernel<<<n_q_heads, 128, 0, s>>>(ws, nrec, G, normalise, static_cast<__half*>(out), out_stride);
+    return launch_status();
+}
+
+int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G, const void* kwin, const void* vwin,
+                         int64_t win_hs, int64_t win_ts, int W, float softmax_scale, float* ws, int rec_index,
+                         unsigned* dev_status, cudaStream_t s) {
+    if (!kwin || !vwin) return MFAR_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(kwin) & 15) || (reinterpret_cast<uintptr_t>(vwin) & 15) || (win_hs & 7) || (win_ts & 7))
+        return MFAR_ERR_ALIGN;
+    DecodeParams p{};
+    p.q = static_cast<const __half*>(q);
+    p.q_stride = q_stride;
+    p.kwin = static_cast<const __half*>(kwin);
+    p.vwin = static_cast<const __half*>(vwin);
+    p.win_hs = win_hs;
+    p.win_ts = win_ts;
+    p.W = W;
+    p.nsplit = rec_index;
+    p.split_offset = rec_index;
+    p.cap = 8;
+    p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    p.ws = ws;
+    p.dev_status = dev_status;
+    return dispatch_decode<MODE_ATTN>(p, G, n_kv_heads, 1, s);
+}
+
 }  // namespace mfar
 
 using namespace mfar;

@@ -162,5 +162,12 @@ struct DecodeParams {
 // 64-token-block kernel (decode.cu) and 256-token-superblock kernel (decode_sb.cu)
 int launch_decode_sb(const DecodeParams& p, int G, int n_kv_heads, cudaStream_t s);
 bool decode_sb_fits(int cap, int G);
+// merge of the split-KV records (normalise = 1) or plain sum (normalise = 0), one CTA per q head
+int launch_combine(const float* ws, int nrec, int G, int normalise, void* out, int64_t out_stride, int n_q_heads,
+                   cudaStream_t s);
+// dense recent-token window as split record `rec_index` of a workspace with rec_index + 1 records per kv head
+int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G, const void* kwin, const void* vwin,
+                         int64_t win_hs, int64_t win_ts, int W, float softmax_scale, float* ws, int rec_index,
+                         unsigned* dev_status, cudaStream_t s);
 
 }  // namespace mfar

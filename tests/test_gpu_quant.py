@@ -1,0 +1,128 @@
+"""GPU parity of the quantised path: compression bit-exact against the golden fixtures
+(reference Triton kernels) and the oracle; ops against dequantise-then-dense (2e-3 rel L2)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+G_DIR = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def bits16(a):
+    return np.ascontiguousarray(a).view(np.uint16)
+
+
+@pytest.fixture(scope="module")
+def m():
+    os.environ["MUSTAFAR_B200_CHECK"] = "1"
+    from mustafar_b200 import compression, compression_quant, ops_quant
+
+    class M:
+        pass
+    M.c, M.cq, M.oq = compression, compression_quant, ops_quant
+    return M
+
+
+@pytest.mark.parametrize("kind", ["key", "value"])
+def test_convert_quant_matches_golden(m, kind):
+    f = np.load(os.path.join(G_DIR, "quant_cases.npz"))
+    names = sorted({k.split("/")[0] for k in f.files})
+    for name in names:
+        x = torch.from_numpy(f[f"{name}/x"]).cuda()
+        if kind == "key":
+            bmp, off, packed, counts, units, scales, zeros = m.cq.convert_key_batched_quant(x, return_metadata=True)
+            assert len(m.cq.convert_key_batched_quant(x)) == 5
+        else:
+            bmp, off, packed, counts, units, scales, zeros = m.cq.convert_value_batched_quant(x)
+        got = dict(bitmaps=bmp, tile_offsets=off, packed=packed, counts=counts, units=units)
+        for key, t in got.items():
+            assert np.array_equal(t.cpu().numpy(), f[f"{name}/{kind}/{key}"]), (name, key)
+        assert np.array_equal(bits16(scales.cpu().numpy()), bits16(f[f"{name}/{kind}/scales"])), name
+        assert np.array_equal(bits16(zeros.cpu().numpy()), bits16(f[f"{name}/{kind}/zeros"])), name
+        assert packed.dtype == torch.int32 and scales.dtype == torch.float16
+
+
+@pytest.mark.parametrize("bits,group", [(2, 64), (4, 64), (2, 32), (4, 32)])
+@pytest.mark.parametrize("kind", ["key", "value"])
+def test_fused_prune_quant_vs_oracle(m, kind, bits, group):
+    k, v = oracle.make_kv(3, 320, seed=oracle.synth.BASE_SEED + 7)
+    x = k if kind == "key" else v
+    want_in = oracle.prune_ref(x, 0.5)
+    fn = oracle.quant_compress_key_ref if kind == "key" else oracle.quant_compress_value_ref
+    want = fn(want_in, bits=bits, group=group)
+    got = m.cq.compress_quant(x.cuda(), m.c.KEY if kind == "key" else m.c.VALUE, m.c.keep_rank(0.5), bits, group)
+    for key in ("bitmaps", "tile_offsets", "counts", "units", "packed"):
+        assert np.array_equal(got[key].cpu().numpy(), want[key]), key
+    for key in ("scales", "zeros"):
+        assert np.array_equal(bits16(got[key].cpu().numpy()), bits16(want[key])), key
+
+
+def build(m, Bh, L, s, bits, group, seed):
+    k, v = oracle.make_kv(Bh, L, seed=seed)
+    kp, vp = oracle.prune_ref(k, s), oracle.prune_ref(v, s)
+    kq = m.cq.compress_quant(k.cuda(), m.c.KEY, m.c.keep_rank(s), bits, group)
+    vq = m.cq.compress_quant(v.cuda(), m.c.VALUE, m.c.keep_rank(s), bits, group)
+    kd = oracle.dequant_key_ref(oracle.quant_compress_key_ref(kp, bits, group), L, bits=bits, group=group)
+    vd = oracle.dequant_value_ref(oracle.quant_compress_value_ref(vp, bits, group), L, bits=bits, group=group)
+    return kq, vq, kd, vd
+
+
+@pytest.mark.parametrize("G,Bh,L,s,bits,group", [
+    (1, 3, 256, 0.7, 2, 64), (4, 2, 512, 0.5, 2, 64), (4, 2, 1024, 0.7, 2, 64), (8, 1, 256, 0.7, 2, 64),
+    (4, 2, 256, 0.7, 4, 64), (4, 2, 256, 0.5, 2, 32), (2, 2, 192, 0.5, 4, 32),
+])
+def test_quant_ops_vs_dequantise_then_dense(m, G, Bh, L, s, bits, group):
+    kq, vq, kd, vd = build(m, Bh, L, s, bits, group, 40 + L)
+    q = oracle.make_query(Bh * G, seed=9 + L)
+    cap = 32 // bits
+    # key op
+    want = oracle.key_formulation_ref(kd, q, G)
+    padded = torch.nn.functional.pad(q.cuda().view(Bh * G, 1, 128), (0, 0, 0, 7))
+    args = (kq["bitmaps"], kq["packed"], kq["tile_offsets"])
+    out = m.oq.mustafar_key_formulation_quant(*args, kq["scales"], kq["zeros"], padded, L, 128, Bh * G, G, bits, cap, 0)
+    assert out.shape == (Bh * G, 8, L)
+    assert oracle.rel_l2(out[:, 0].cpu(), want) < TOL
+    out2 = m.oq.mustafar_key_formulation_quant_meta(*args, kq["counts"], kq["units"], kq["scales"], kq["zeros"], padded,
+                                                    L, 128, Bh * G, G, bits, cap, 1)
+    assert torch.equal(out, out2)
+    # value ops
+    gen = torch.Generator().manual_seed(L)
+    p = torch.softmax(torch.randn(Bh * G, L, generator=gen) * 3, dim=-1).half()
+    want_v = oracle.value_formulation_ref(vd, p, G)
+    pp = torch.nn.functional.pad(p.cuda().view(Bh * G, 1, L), (0, 0, 0, 7)).contiguous()
+    ws = torch.zeros(1, dtype=torch.float16, device="cuda")
+    vargs = (vq["bitmaps"], vq["packed"], vq["tile_offsets"], vq["counts"], vq["units"], vq["scales"], vq["zeros"])
+    o1 = m.oq.mustafar_value_formulation_quant(*vargs, pp, ws, 128, L, Bh * G, G, bits, cap, 0, 4, 2)
+    assert o1.shape == (Bh * G, 8, 128)
+    assert oracle.rel_l2(o1[:, 0].cpu(), want_v) < TOL
+    o2 = m.oq.mustafar_value_formulation_quant_decode_n1(*vargs, p.cuda(), ws, 128, L, Bh * G, G, bits, cap, 0, 4)
+    assert o2.shape == (Bh * G, 128)
+    assert oracle.rel_l2(o2.cpu(), want_v) < TOL
+    assert m.oq.mustafar_quant_sparse_forward is m.oq.mustafar_key_formulation_quant
+
+
+@pytest.mark.parametrize("G,Bh,L,W,s,bits,group", [
+    (4, 8, 2048, 128, 0.7, 2, 64), (4, 2, 512, 200, 0.5, 2, 64), (1, 4, 256, 0, 0.7, 2, 64),
+    (4, 2, 256, 128, 0.7, 4, 64), (4, 2, 256, 128, 0.5, 2, 32), (4, 2, 0, 130, 0.7, 2, 64),
+])
+def test_fused_quant_attention(m, G, Bh, L, W, s, bits, group):
+    if L:
+        kq, vq, kd, vd = build(m, Bh, L, s, bits, group, 60 + L + W)
+    else:
+        kq = vq = dict(bitmaps=torch.zeros(Bh, 0, dtype=torch.int64, device="cuda"),
+                       tile_offsets=torch.zeros(Bh, 0, dtype=torch.int32, device="cuda"),
+                       scales=torch.zeros(Bh, 0, dtype=torch.float16, device="cuda"),
+                       zeros=torch.zeros(Bh, 0, dtype=torch.float16, device="cuda"),
+                       packed=torch.zeros(1, dtype=torch.int32, device="cuda"))
+        kd = vd = torch.zeros(Bh, 0, 128, dtype=torch.float16)
+    kw, vw = oracle.make_kv(Bh, max(W, 1), seed=70 + W)
+    kw, vw = kw[:, :W], vw[:, :W]
+    q = oracle.make_query(Bh * G, seed=3 + L)
+    want = oracle.decode_attention_ref(q, kd, vd, kw, vw, G)
+    out = m.oq.decode_attention_quant(q.cuda(), kq, vq, L, kw.cuda() if W else None, vw.cuda() if W else None, G, bits)
+    assert oracle.rel_l2(out.float().cpu(), want) < TOL
