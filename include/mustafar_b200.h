@@ -92,6 +92,23 @@ int mfar_compress_fp16(const void* x, int64_t x_head_stride, int64_t x_token_str
                        void* scratch, size_t scratch_bytes,
                        uint32_t* dev_status, uint32_t* max_block_halves, void* stream);
 
+/* The same compression for callers that cannot provide a scratch buffer because they may not
+ * allocate device memory while running (a server that hands out all GPU memory from its own arena at
+ * start-up, a plugin inside another runtime's budget).  No counterpart in the reference.
+ * The look-back scratch is a fixed array inside the library (64 KiB + 16 B per GPU, held until the
+ * process exits), which limits one call to n_heads * (n_tokens / 64) <= MFAR_NOALLOC_MAX_BLOCKS;
+ * larger jobs return MFAR_ERR_LIMIT without launching.  Calls on one device share that array: each call
+ * clears what it uses, but calls that could overlap on the GPU race and must be ordered by the caller.
+ * The first call on a device resolves the array's address; issue it before any stream capture. */
+#define MFAR_NOALLOC_MAX_BLOCKS 8192
+int mfar_compress_fp16_noalloc(const void* x, int64_t x_head_stride, int64_t x_token_stride,
+                               int n_heads, int n_tokens, int kind, int prune_rank,
+                               int64_t* bitmaps, int64_t bmp_head_stride,
+                               int32_t* accum, int64_t acc_head_stride, int64_t tile_start,
+                               void* nz, const int32_t* nz_offset, int64_t nz_head_stride,
+                               int64_t nz_capacity, uint32_t* dev_status, uint32_t* max_block_halves,
+                               void* stream);
+
 /* Prune only (writes x * (|x| >= thr) with the reference's signed zeros).
  * Replaces models/llama_mustafar_kernel.py:194-232.  In place allowed (y == x). */
 int mfar_prune_fp16(const void* x, void* y, int64_t n_rows, int64_t row_stride,

@@ -249,3 +249,48 @@ extern "C" int mfar_prune_fp16(const void* x, void* y, int64_t n_rows, int64_t r
         static_cast<const __half*>(x), static_cast<__half*>(y), n_rows, row_stride, prune_rank);
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of mfar_compress_fp16.
+//
+// Some hosts may not call cudaMalloc at all while they run: an inference server whose device
+// memory is handed out once at start-up by its own arena, or a plugin that lives inside another
+// runtime's memory budget and has nowhere to keep a scratch buffer of its own.  For those callers
+// the ticket counter and the per-block status words of the look-back live in a fixed array inside
+// this library's device image instead of a caller-provided buffer.
+//
+// The array costs kStaticScratchBytes of device memory on every GPU that loads the library, for
+// as long as the process lives.  It bounds the job size: n_heads * (n_tokens / 64) must not exceed
+// MFAR_NOALLOC_MAX_BLOCKS, otherwise MFAR_ERR_LIMIT is returned and nothing is launched.
+//
+// All calls on one device share the array.  Each call first clears the part it uses (on `stream`),
+// so leftovers of an earlier call never matter; two calls that may overlap on the GPU (different
+// streams without an ordering between them) would corrupt each other's tickets and must not be issued.
+//
+// The first call on a device looks the array's device address up (cudaGetSymbolAddress with that
+// device current) and remembers it; make that first call outside any stream capture.
+constexpr size_t kStaticScratchBytes = 16 + 8 * static_cast<size_t>(MFAR_NOALLOC_MAX_BLOCKS);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static void* g_static_scratch_addr[64] = {nullptr};   // per device; a host-side name is not a device address
+
+extern "C" int mfar_compress_fp16_noalloc(const void* x, int64_t x_head_stride, int64_t x_token_stride,
+                                          int n_heads, int n_tokens, int kind, int prune_rank,
+                                          int64_t* bitmaps, int64_t bmp_head_stride,
+                                          int32_t* accum, int64_t acc_head_stride, int64_t tile_start,
+                                          void* nz, const int32_t* nz_offset, int64_t nz_head_stride,
+                                          int64_t nz_capacity, uint32_t* dev_status, uint32_t* max_block_halves,
+                                          void* stream) {
+    if (n_heads < 0 || n_tokens < 0 || (n_tokens % 64) != 0) return MFAR_ERR_ARG;
+    if (static_cast<int64_t>(n_heads) * (n_tokens / 64) > MFAR_NOALLOC_MAX_BLOCKS) return MFAR_ERR_LIMIT;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MFAR_ERR_LAUNCH;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_static_scratch) != cudaSuccess || addr == nullptr) return MFAR_ERR_LAUNCH;
+        g_static_scratch_addr[dev] = addr;
+    }
+    return mfar_compress_fp16(x, x_head_stride, x_token_stride, n_heads, n_tokens, kind, prune_rank, bitmaps,
+                              bmp_head_stride, accum, acc_head_stride, tile_start, nz, nz_offset, nz_head_stride,
+                              nz_capacity, g_static_scratch_addr[dev], kStaticScratchBytes, dev_status,
+                              max_block_halves, stream);
+}
