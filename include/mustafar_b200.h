@@ -45,7 +45,8 @@ typedef enum {
 #define MFAR_DEV_BADMETA 4u    /* offsets in the cache are inconsistent           */
 
 enum { MFAR_KIND_KEY = 0, MFAR_KIND_VALUE = 1 };
-enum { MFAR_DECODE_FORCE_BLOCK = 1, MFAR_DECODE_FORCE_SUPERBLOCK = 2 };
+enum { MFAR_DECODE_FORCE_BLOCK = 1, MFAR_DECODE_FORCE_SUPERBLOCK = 2, MFAR_DECODE_FORCE_STREAM = 4,
+       MFAR_DECODE_FP16_COEF = 8 /* stream kernel: q and the probabilities enter the FMA as fp16 */ };
 
 int mfar_version(void);
 const char* mfar_status_string(int status);

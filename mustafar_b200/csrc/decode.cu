@@ -607,8 +607,23 @@ extern "C" int mfar_decode_attention_fp16(
     (void)nsb;
     if ((flags & MFAR_DECODE_FORCE_SUPERBLOCK) && p.nblk > 0 && decode_sb_fits(p.cap, group)) use_sb = true;
 
+    const bool use_stream = (flags & MFAR_DECODE_FORCE_STREAM) && p.nblk > 0;
     int nrec;
-    if (use_sb) {
+    if (use_stream) {
+        const int mb = decode_stream_max_blocks();
+        if (ns * mb < p.nblk) ns = (p.nblk + mb - 1) / mb;
+        p.bps = (p.nblk + ns - 1) / ns;
+        ns = (p.nblk + p.bps - 1) / p.bps;
+        p.nsplit = ns;
+        nrec = ns + (window > 0 ? 1 : 0);
+        r = launch_decode_stream(p, group, n_kv_heads, (flags & MFAR_DECODE_FP16_COEF) != 0, s);
+        if (r) return r;
+        if (window > 0) {
+            r = launch_window_record(q, q_stride, n_kv_heads, group, k_window, v_window, win_head_stride,
+                                     win_token_stride, window, softmax_scale, p.ws, ns, dev_status, s);
+            if (r) return r;
+        }
+    } else if (use_sb) {
         int sps = 0;
         sb_split(n_kv_heads, p.nblk, nsplit, &ns, &sps);
         p.nsplit = ns;

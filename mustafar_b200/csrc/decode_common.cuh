@@ -162,6 +162,9 @@ struct DecodeParams {
 // 64-token-block kernel (decode.cu) and 256-token-superblock kernel (decode_sb.cu)
 int launch_decode_sb(const DecodeParams& p, int G, int n_kv_heads, cudaStream_t s);
 bool decode_sb_fits(int cap, int G);
+// barrier-free 64-token-block kernel (decode_stream.cu); mixed = fp16 coefficients, one mixed-precision FMA per head
+int launch_decode_stream(const DecodeParams& p, int G, int n_kv_heads, bool mixed, cudaStream_t s);
+int decode_stream_max_blocks();
 // merge of the split-KV records (normalise = 1) or plain sum (normalise = 0), one CTA per q head
 int launch_combine(const float* ws, int nrec, int G, int normalise, void* out, int64_t out_stride, int n_q_heads,
                    cudaStream_t s);
