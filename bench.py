@@ -153,7 +153,7 @@ def algorithmic_bytes(ks, vs, window, batch):
 
 
 # ------------------------------------------------------------------------------------------ CPU baseline
-def cpu_baseline(kv_len, window, sparsity, budget_s):
+def cpu_baseline(kv_len, window, sparsity, budget_s, steps=None, warmup=3):
     """The reference's torch path on the host cores (oracle port): dense
     softmax(q.K~^T / sqrt(d)).V~ on the pruned tensors for ONE sequence (8 kv heads,
     32 q heads) of the same length; K~/V~ held in fp32 so the step is pure attention."""
@@ -172,10 +172,15 @@ def cpu_baseline(kv_len, window, sparsity, budget_s):
         p = torch.softmax(s, dim=-1)
         return torch.bmm(p.unsqueeze(1), vv).squeeze(1)
 
-    for _ in range(3):
+    for _ in range(max(1, warmup)):
         step()
     times, t_end = [], time.perf_counter() + budget_s
-    while len(times) < 10 or (time.perf_counter() < t_end and len(times) < 200):
+    if steps is not None:                      # reference arm: exactly `steps` timed steps
+        for _ in range(steps):
+            t0 = time.perf_counter()
+            step()
+            times.append(time.perf_counter() - t0)
+    while steps is None and (len(times) < 10 or (time.perf_counter() < t_end and len(times) < 200)):
         t0 = time.perf_counter()
         step()
         times.append(time.perf_counter() - t0)
@@ -202,7 +207,7 @@ def main():
     if a.impl == "reference":
         if rank != 0:
             return
-        cb = cpu_baseline(a.kv_len, a.window, a.sparsity, max(5.0, min(120.0, a.cpu_seconds * 2)))
+        cb = cpu_baseline(a.kv_len, a.window, a.sparsity, a.cpu_seconds, steps=a.steps, warmup=a.warmup)
         line = {"impl": "reference", "metric": "sparse_decode_attention_throughput", "value": cb["value"],
                 "unit": "tok/s/layer", "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
                 "ms_per_step": cb["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -294,11 +299,14 @@ def main():
             "clocks": clocks.summary(),
             "e2e": {"value": world * a.batch * a.steps / (e2e_ms * 1e-3), "unit": "tok/s/layer",
                     "h2d_bytes_per_step": q.numel() * 2, "d2h_bytes_per_step": out.numel() * 2},
-            "gpu_launches": 2 * a.steps,
+            "gpu_launches": (3 if a.variant.startswith("stream") or a.variant == "superblock" else 2) * a.steps,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": which, "frac_of_nominal_8000": achieved / 8000.0,
-                         "algorithmic_bytes_per_launch": alg_bytes, "traffic": None,
-                         "kernel": "decode_kernel<G=4,ATTN> (+ combine_kernel, <1 % of the step)"},
+                         "algorithmic_bytes_per_launch": alg_bytes,
+                         # dram__bytes_read+write of one launch in the ncu capture of the B=16, L=8192 case
+                         # (265.0 MB for 256.9 MB algorithmic), scaled by the units of this launch
+                         "traffic": alg_bytes * (265.0 / 256.9),
+                         "kernel": "decode kernel, variant %s (+ combine_kernel, <1 %% of the step)" % a.variant},
         }
         if not a.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(a.kv_len, a.window, a.sparsity, a.cpu_seconds)
