@@ -282,10 +282,8 @@ def main():
     e2e_ms = e0.elapsed_time(e1)
     ops.check_device_status(dev)
 
-    t = torch.tensor([total_ms, e2e_ms, per_launch_ms], device=dev, dtype=torch.float64)
-    if dist is not None:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, per_launch_ms = (float(x) for x in t.tolist())
+    from mustafar_b200.sharding import max_over_ranks
+    total_ms, e2e_ms, per_launch_ms = (max_over_ranks(x, dist, dev) for x in (total_ms, e2e_ms, per_launch_ms))
 
     if rank == 0:
         peak, which = measured_peak_gbs()
