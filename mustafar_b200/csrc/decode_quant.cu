@@ -9,9 +9,9 @@
 //     fixed slot of a double-buffered shared-memory block, one block ahead of the compute;
 //   * a lane extracts a 32-bit window of codes that starts at its first rank with one funnel
 //     shift; every set bit consumes `bits` bits of the window;
-//   * value = fp16((code - zero) * scale) in fp32 arithmetic, exactly what the reference
-//     places in shared memory (kernel_quant/csrc/SpMM_Kernel_Quant.cuh:235-240), then one
-//     mixed-precision FMA per head (fp16 value x fp16 coefficient, fp32 accumulate).
+//   * value = (code - zero) * scale in fp32 (the reference's mode-0 arithmetic,
+//     kernel_quant/csrc/SpMM_Kernel_Quant.cuh:235-240, without its re-rounding of the product to
+//     fp16), with the scale folded into the per-tile coefficients; fp32 accumulation.
 #include "decode_common.cuh"
 
 namespace mfar {
@@ -51,11 +51,6 @@ __device__ __forceinline__ void cp_async4(void* dst_smem, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-__device__ __forceinline__ float fma_f16(float acc, unsigned short a, unsigned short b) {
-    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc) : "h"(a), "h"(b));
-    return acc;
-}
-
 template <int BITS>
 struct QBuf {   // one staged tensor of one 64-token block
     static constexpr int WPT = 64 * BITS / 32;   // words per tile slot
@@ -64,53 +59,49 @@ struct QBuf {   // one staged tensor of one 64-token block
     unsigned words[128 * WPT + 4];
 };
 
+// One tile step over quantised codes.  The dequantised value (code - zero) * scale is never
+// materialised: per tile the lane folds the scale into the G coefficients (sc[g] = scale * coef[g])
+// and per set bit computes d = code - zero exactly (the code is turned into a float by or-ing it into
+// the mantissa of 2^23) and accumulates d * sc[g] in fp32.
 template <int G, int BITS, bool GROUP32>
 __device__ __forceinline__ void tile_step_q(unsigned hi, unsigned lo, const unsigned* words, const unsigned* sz,
                                             unsigned sel, unsigned mh, unsigned ml,
-                                            const unsigned short (&coef)[G], float (&acc)[8][G]) {
+                                            const float (&coef)[G], float (&acc)[8][G]) {
     constexpr unsigned MASK = (1u << BITS) - 1u;
     const unsigned byte = __byte_perm(lo, hi, sel);
     int rank = __popc(hi & mh) + __popc(lo & ml);
     const unsigned bitoff = static_cast<unsigned>(rank) * BITS;
     unsigned window = __funnelshift_r(words[bitoff >> 5], words[(bitoff >> 5) + 1], bitoff & 31u);
     const unsigned sz0 = sz[0];
-    float s0 = __half2float(__ushort_as_half(static_cast<unsigned short>(sz0 & 0xffffu)));
-    float z0 = __half2float(__ushort_as_half(static_cast<unsigned short>(sz0 >> 16)));
-    float s1 = s0, z1 = z0;
-    if (GROUP32) {
-        const unsigned sz1 = sz[1];
-        s1 = __half2float(__ushort_as_half(static_cast<unsigned short>(sz1 & 0xffffu)));
-        z1 = __half2float(__ushort_as_half(static_cast<unsigned short>(sz1 >> 16)));
-    }
+    const float s0 = __half2float(__ushort_as_half(static_cast<unsigned short>(sz0 & 0xffffu)));
+    const float zz0 = 8388608.f + __half2float(__ushort_as_half(static_cast<unsigned short>(sz0 >> 16)));
+    if (!GROUP32) {
+        float sc[G];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        if (byte & (0x80u >> i)) {
-            const float c = __uint_as_float(0x4b000000u | (window & MASK)) - 8388608.f;   // exact int -> float
-            window >>= BITS;
-            float s = s0, z = z0;
-            if (GROUP32) {
-                if (rank >= 32) { s = s1; z = z1; }
-                ++rank;
+        for (int g = 0; g < G; ++g) sc[g] = s0 * coef[g];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            if (byte & (0x80u >> i)) {
+                const float d = __uint_as_float(0x4b000000u | (window & MASK)) - zz0;
+                window >>= BITS;
+#pragma unroll
+                for (int g = 0; g < G; ++g) acc[i][g] = fmaf(d, sc[g], acc[i][g]);
             }
-            const unsigned short v = __half_as_ushort(__float2half_rn(__fmul_rn(__fsub_rn(c, z), s)));
-#pragma unroll
-            for (int g = 0; g < G; ++g) acc[i][g] = fma_f16(acc[i][g], v, coef[g]);
         }
-    }
-}
-
-template <int G>
-__device__ __forceinline__ void load_coef_h(const unsigned short* p, unsigned short (&c)[G]) {
-    if constexpr (G == 1) {
-        c[0] = p[0];
-    } else if constexpr (G == 2) {
-        const unsigned t = *reinterpret_cast<const unsigned*>(p);
-        c[0] = t & 0xffffu; c[1] = t >> 16;
     } else {
+        const unsigned sz1 = sz[1];
+        const float s1 = __half2float(__ushort_as_half(static_cast<unsigned short>(sz1 & 0xffffu)));
+        const float zz1 = 8388608.f + __half2float(__ushort_as_half(static_cast<unsigned short>(sz1 >> 16)));
 #pragma unroll
-        for (int g = 0; g < G; g += 4) {
-            const uint2 t = *reinterpret_cast<const uint2*>(p + g);
-            c[g] = t.x & 0xffffu; c[g + 1] = t.x >> 16; c[g + 2] = t.y & 0xffffu; c[g + 3] = t.y >> 16;
+        for (int i = 0; i < 8; ++i) {
+            if (byte & (0x80u >> i)) {
+                const bool second = rank >= 32;      // nonzeros 32.. of the tile use the second scale / zero
+                ++rank;
+                const float d = (__uint_as_float(0x4b000000u | (window & MASK)) - (second ? zz1 : zz0)) * (second ? s1 : s0);
+                window >>= BITS;
+#pragma unroll
+                for (int g = 0; g < G; ++g) acc[i][g] = fmaf(d, coef[g], acc[i][g]);
+            }
         }
     }
 }
@@ -122,9 +113,9 @@ struct QLayout {
         size_t o = 0;
         kbuf = o; o += (MODE != MODE_VALUE) ? 2 * sizeof(QBuf<BITS>) : 0;
         vbuf = o; o += (MODE != MODE_KEY) ? 2 * sizeof(QBuf<BITS>) : 0;
-        qh = o;    o += kD * G * 2;
+        qh = o;    o += kD * G * 4;
         spart = o; o += static_cast<size_t>(kQPlanes) * G * 64 * 4;
-        ps = o;    o += 64 * G * 2 + 64;
+        ps = o;    o += 64 * G * 4 + 64;
         alpha = o; o += 64;
         total = o;
     }
@@ -138,9 +129,9 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
     const QLayout<G, MODE, BITS> lay;
     QBuf<BITS>* kbuf = reinterpret_cast<QBuf<BITS>*>(smem + lay.kbuf);
     QBuf<BITS>* vbuf = reinterpret_cast<QBuf<BITS>*>(smem + lay.vbuf);
-    unsigned short* qh = reinterpret_cast<unsigned short*>(smem + lay.qh);   // [128][G]
+    float* qh = reinterpret_cast<float*>(smem + lay.qh);                    // [128][G]
     float* spart = reinterpret_cast<float*>(smem + lay.spart);              // [plane][G][64]
-    unsigned short* ps = reinterpret_cast<unsigned short*>(smem + lay.ps);  // [64][G] fp16
+    float* ps = reinterpret_cast<float*>(smem + lay.ps);                    // [64][G]
     float* alpha_s = reinterpret_cast<float*>(smem + lay.alpha);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -155,7 +146,7 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
     if (MODE != MODE_VALUE) {
         for (int i = tid; i < kD * G; i += kQThreads) {
             const int c = i / G, g = i % G;
-            qh[i] = __half_as_ushort(p.q[(static_cast<int64_t>(h) * G + g) * p.q_stride + c]);
+            qh[i] = __half2float(p.q[(static_cast<int64_t>(h) * G + g) * p.q_stride + c]);
         }
     }
 
@@ -231,8 +222,8 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
             for (int s = 0; s < 32 / 4; ++s) {
                 const int c = warp * 32 + s * 4 + gi;
                 const uint2 bm = kbf.bm[c];
-                unsigned short coef[G];
-                load_coef_h<G>(qh + c * G, coef);
+                float coef[G];
+                load_coef<G>(qh + c * G, coef);
                 tile_step_q<G, BITS, GROUP32>(bm.y, bm.x, kbf.words + c * WPT, kbf.sz + 2 * c, sel, mh, ml, coef, acc_s);
             }
             float* dst = spart + (static_cast<size_t>(warp * 4 + gi) * G) * 64 + kb * 8;
@@ -249,8 +240,8 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
             for (int g = warp; g < G; g += kQWarps) {
                 const unsigned pv = *reinterpret_cast<const unsigned*>(
                     p.p_in + (static_cast<int64_t>(h) * G + g) * p.p_stride + static_cast<int64_t>(blk0 + i) * 64 + 2 * lane);
-                ps[(2 * lane) * G + g] = pv & 0xffffu;
-                ps[(2 * lane + 1) * G + g] = pv >> 16;
+                ps[(2 * lane) * G + g] = __half2float(__ushort_as_half(static_cast<unsigned short>(pv & 0xffffu)));
+                ps[(2 * lane + 1) * G + g] = __half2float(__ushort_as_half(static_cast<unsigned short>(pv >> 16)));
             }
         } else {
 #pragma unroll
@@ -272,12 +263,11 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
                         s1 *= p.scale_log2;
                         const float m_new = fmaxf(m_run[j], warp_max_f32(fmaxf(s0, s1)));
                         const float a = fast_exp2(m_run[j] - m_new);
-                        // the probabilities are rounded to fp16 before P.V, as the reference model does
-                        const __half h0 = __float2half_rn(fast_exp2(s0 - m_new)), h1 = __float2half_rn(fast_exp2(s1 - m_new));
-                        l_run[j] = l_run[j] * a + (__half2float(h0) + __half2float(h1));
+                        const float p0 = fast_exp2(s0 - m_new), p1 = fast_exp2(s1 - m_new);
+                        l_run[j] = l_run[j] * a + (p0 + p1);
                         m_run[j] = m_new;
-                        ps[(2 * lane) * G + g] = __half_as_ushort(h0);
-                        ps[(2 * lane + 1) * G + g] = __half_as_ushort(h1);
+                        ps[(2 * lane) * G + g] = p0;
+                        ps[(2 * lane + 1) * G + g] = p1;
                         if (lane == 0) alpha_s[g] = a;
                     }
                 }
@@ -305,8 +295,8 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
             const int t = warp * 16 + s * 2 + par;
             const int tile = half_id * 64 + t;
             const uint2 bm = vbf.bm[tile];
-            unsigned short coef[G];
-            load_coef_h<G>(ps + t * G, coef);
+            float coef[G];
+            load_coef<G>(ps + t * G, coef);
             tile_step_q<G, BITS, GROUP32>(bm.y, bm.x, vbf.words + tile * WPT, vbf.sz + 2 * tile, sel, mh, ml, coef, acc_o);
         }
     }
