@@ -1,0 +1,81 @@
+"""End-to-end decode benchmark of the Llama-3-8B-shaped model with the sparse KV cache.
+
+    python -m mustafar_b200.e2e_llama [--batch 32] [--prompt 4096] [--new 256] [--parallel tp|dp]
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m mustafar_b200.e2e_llama --parallel tp
+
+Random-init fp16 weights (seeded), uniformly random prompt ids, greedy decoding.  `tp` = 8-way
+(or world-size-way) head tensor parallelism with an NCCL all-reduce after o_proj and down_proj;
+`dp` = every rank runs the whole model on its own `--batch` sequences (no collective).
+Prints one JSON line on rank 0: prefill time, time per output token and decode tokens/s of the
+whole job, measured with CUDA events, maximum over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from .llama_shape import LlamaShape, SparseLlama
+from .sharding import max_over_ranks
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--prompt", type=int, default=4096)
+    ap.add_argument("--new", type=int, default=256)
+    ap.add_argument("--parallel", default="dp", choices=["tp", "dp"])
+    ap.add_argument("--sparsity", type=float, default=0.7)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--dense", action="store_true", help="dense pruned cache + torch attention (comparison arm)")
+    a = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    tp = world if a.parallel == "tp" else 1
+    shape = LlamaShape(n_layers=a.layers)
+    model = SparseLlama(shape, a.batch, a.prompt + a.new, dev, sparsity=a.sparsity, seed=1234,
+                        tp_rank=rank if tp > 1 else 0, tp_world=tp, dist=dist, sparse=not a.dense)
+    g = torch.Generator(device=dev).manual_seed(99 if tp > 1 else 99 + rank)
+    toks = torch.randint(0, shape.vocab, (a.batch, a.prompt), generator=g, device=dev)
+
+    def sync():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sync()
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    e[0].record()
+    nxt = model.prefill(toks).argmax(-1)
+    e[1].record()
+    for _ in range(a.new - 1):
+        nxt = model.decode_step(nxt).argmax(-1)
+    e[2].record()
+    torch.cuda.synchronize()
+    prefill_ms = max_over_ranks(e[0].elapsed_time(e[1]), dist, dev)
+    decode_ms = max_over_ranks(e[1].elapsed_time(e[2]), dist, dev)
+    seqs = a.batch * (1 if tp > 1 else world)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "llama3_8b_shape_decode_throughput", "unit": "tok/s", "n_gpus": world,
+            "value": seqs * (a.new - 1) / (decode_ms * 1e-3), "tpot_ms": decode_ms / (a.new - 1), "ttft_ms": prefill_ms,
+            "config": {"workload": f"Llama-3-8B shape, {a.layers} layers, prompt {a.prompt}, {a.new} new tokens, "
+                                   f"batch {a.batch} per {'job' if tp > 1 else 'GPU'}, sparsity {a.sparsity}, window 128",
+                       "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}", "cache": "dense-pruned torch" if a.dense else "sparse fp16"},
+            "data": "synthetic (random-init weights, random prompt ids)", "dtype": "f16"}))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

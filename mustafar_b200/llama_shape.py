@@ -1,0 +1,241 @@
+"""Llama-3-8B-shaped decoder that keeps its KV cache in the sparse format and decodes through
+the fused attention entry (the patched counterpart of the reference's model glue,
+``models/llama_mustafar_kernel.py:320-599``, not an edit of it).
+
+What differs from the reference layer:
+  * the cache is a pair of preallocated ``SparseStore`` arenas per layer plus a fixed-capacity dense
+    window; nothing is ``torch.cat``-ed, padded to 8 rows or copied per step;
+  * prune and compression are one kernel (prefill: the first ``((T - residual) // 256) * 256``
+    tokens, ``:540-557``; decode: the oldest 256 tokens whenever the window reaches
+    ``residual + 256``, ``:445-519``);
+  * q.K^T over compressed + window, softmax and P.V are one call per layer per step.
+Linear layers, RMSNorm, RoPE and the dense causal prefill attention are plain torch (cuBLAS /
+SDPA); they are outside the hot path this package accelerates.
+
+Weights are random (normal, std 0.02, seeded) with the Llama-3-8B shapes; with tensor parallelism
+every rank slices the SAME full matrices by head (q/k/v/gate/up by column, o/down by row) and the
+partial sums meet in an NCCL all-reduce after ``o_proj`` and ``down_proj``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import compression as comp
+from . import ops
+
+D = 128
+
+
+@dataclass
+class LlamaShape:
+    hidden: int = 4096
+    n_layers: int = 32
+    n_q_heads: int = 32
+    n_kv_heads: int = 8
+    ffn: int = 14336
+    vocab: int = 128256
+    rope_theta: float = 500000.0
+    rms_eps: float = 1e-5
+
+
+def tiny_shape() -> LlamaShape:
+    """Same head layout (head_dim 128, 4 q heads per kv head), small everything else: for tests."""
+    return LlamaShape(hidden=256, n_layers=2, n_q_heads=8, n_kv_heads=2, ffn=512, vocab=1000)
+
+
+def _rms(x, w, eps):
+    v = x.float()
+    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+def _rope(x, pos, theta):
+    """x [..., T, D] with positions pos [T] (rotate-half convention)."""
+    half = x.shape[-1] // 2
+    inv = 1.0 / (theta ** (torch.arange(0, half, device=x.device, dtype=torch.float32) / half))
+    ang = pos.float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().to(x.dtype), ang.sin().to(x.dtype)
+    x1, x2 = x[..., :half], x[..., half:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+
+class _Layer:
+    __slots__ = ("wqkv", "wo", "wgu", "wd", "n1", "n2", "ks", "vs", "kwin", "vwin")
+
+
+class SparseLlama:
+    """Inference-only model object; one instance per rank."""
+
+    def __init__(self, shape: LlamaShape, batch: int, max_tokens: int, device, sparsity: float = 0.7,
+                 residual: int = 128, seed: int = 0, tp_rank: int = 0, tp_world: int = 1, dist=None,
+                 sparse: bool = True):
+        assert shape.n_kv_heads % tp_world == 0 and shape.ffn % tp_world == 0
+        self.s, self.B, self.dev = shape, batch, torch.device(device)
+        self.sparsity, self.residual, self.sparse = sparsity, residual, sparse
+        self.tp_rank, self.tp_world, self.dist = tp_rank, tp_world, dist
+        self.hq = shape.n_q_heads // tp_world
+        self.hkv = shape.n_kv_heads // tp_world
+        self.G = shape.n_q_heads // shape.n_kv_heads
+        self.max_tokens = (max_tokens + 255) // 256 * 256
+        self.wcap = residual + 256
+        self.rank_keep = comp.keep_rank(sparsity)
+        self.tokens = 0          # tokens seen so far
+        self.compressed = 0      # of which compressed
+        self.wlen = 0            # tokens in the dense window
+        g = torch.Generator(device=self.dev).manual_seed(seed)
+
+        def rnd(*shape_):
+            return (torch.randn(*shape_, generator=g, device=self.dev, dtype=torch.float32) * 0.02).half()
+
+        hd, f = shape.hidden, shape.ffn
+        fl = f // tp_world
+        q0, k0 = tp_rank * self.hq * D, tp_rank * self.hkv * D
+        self.embed = rnd(shape.vocab, hd)
+        self.lm_head = rnd(shape.vocab, hd)
+        self.norm = torch.ones(hd, dtype=torch.float16, device=self.dev)
+        self.layers = []
+        Bh = batch * self.hkv
+        for _ in range(shape.n_layers):
+            L = _Layer()
+            wq, wk, wv = rnd(shape.n_q_heads * D, hd), rnd(shape.n_kv_heads * D, hd), rnd(shape.n_kv_heads * D, hd)
+            L.wqkv = torch.cat([wq[q0:q0 + self.hq * D], wk[k0:k0 + self.hkv * D], wv[k0:k0 + self.hkv * D]]).contiguous()
+            L.wo = rnd(hd, shape.n_q_heads * D)[:, q0:q0 + self.hq * D].contiguous()
+            wg, wu = rnd(f, hd), rnd(f, hd)
+            L.wgu = torch.cat([wg[tp_rank * fl:(tp_rank + 1) * fl], wu[tp_rank * fl:(tp_rank + 1) * fl]]).contiguous()
+            L.wd = rnd(hd, f)[:, tp_rank * fl:(tp_rank + 1) * fl].contiguous()
+            L.n1 = torch.ones(hd, dtype=torch.float16, device=self.dev)
+            L.n2 = torch.ones(hd, dtype=torch.float16, device=self.dev)
+            del wq, wk, wv, wg, wu
+            if sparse:
+                cap = int(self.max_tokens * D * min(1.0, (1.0 - sparsity) + 0.25)) // 8 * 8
+                L.ks = comp.SparseStore(Bh, self.max_tokens, comp.KEY, self.dev, nz_capacity=cap)
+                L.vs = comp.SparseStore(Bh, self.max_tokens, comp.VALUE, self.dev, nz_capacity=cap)
+                L.kwin = torch.empty(Bh, self.wcap, D, dtype=torch.float16, device=self.dev)
+                L.vwin = torch.empty(Bh, self.wcap, D, dtype=torch.float16, device=self.dev)
+            else:   # dense reference cache: pruned tokens kept with their zeros (the torch accuracy path)
+                L.ks = torch.empty(Bh, self.max_tokens + self.wcap, D, dtype=torch.float16, device=self.dev)
+                L.vs = torch.empty(Bh, self.max_tokens + self.wcap, D, dtype=torch.float16, device=self.dev)
+                L.kwin = L.vwin = None
+            self.layers.append(L)
+        self._stage_hint = None
+
+    # ------------------------------------------------------------------ pieces
+    def _allreduce(self, x):
+        if self.tp_world > 1:
+            self.dist.all_reduce(x)
+        return x
+
+    def _mlp(self, L, x):
+        gu = F.linear(x, L.wgu)
+        fl = gu.shape[-1] // 2
+        return self._allreduce(F.linear(F.silu(gu[..., :fl]) * gu[..., fl:], L.wd))
+
+    def _qkv(self, L, x, pos):
+        """x [B, T, hidden] -> q [B, hq, T, D], k, v [B, hkv, T, D] with RoPE applied to q and k."""
+        B, T, _ = x.shape
+        qkv = F.linear(x, L.wqkv)
+        q, k, v = qkv.split([self.hq * D, self.hkv * D, self.hkv * D], dim=-1)
+        q = _rope(q.view(B, T, self.hq, D).transpose(1, 2), pos, self.s.rope_theta)
+        k = _rope(k.view(B, T, self.hkv, D).transpose(1, 2), pos, self.s.rope_theta)
+        return q, k, v.view(B, T, self.hkv, D).transpose(1, 2)
+
+    def _logits(self, x):
+        return F.linear(_rms(x, self.norm, self.s.rms_eps), self.lm_head)
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
+        """tokens [B, T] -> logits of the last position [B, vocab]; fills the caches."""
+        B, T = tokens.shape
+        assert B == self.B and self.tokens == 0 and T <= self.max_tokens + self.residual
+        pos = torch.arange(T, device=self.dev)
+        Lc = max(0, (T - self.residual) // 256) * 256
+        x = self.embed[tokens]
+        for L in self.layers:
+            h = _rms(x, L.n1, self.s.rms_eps)
+            q, k, v = self._qkv(L, h, pos)
+            att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            x = x + self._allreduce(F.linear(att.transpose(1, 2).reshape(B, T, self.hq * D), L.wo))
+            x = x + self._mlp(L, _rms(x, L.n2, self.s.rms_eps))
+            kf, vf = k.reshape(B * self.hkv, T, D), v.reshape(B * self.hkv, T, D)
+            if self.sparse:
+                if Lc:
+                    L.ks.append(kf[:, :Lc], self.rank_keep)       # strided views: no copy
+                    L.vs.append(vf[:, :Lc], self.rank_keep)
+                L.kwin[:, :T - Lc] = kf[:, Lc:]
+                L.vwin[:, :T - Lc] = vf[:, Lc:]
+            else:
+                L.ks[:, :T], L.vs[:, :T] = kf, vf
+                if Lc:
+                    L.ks[:, :Lc] = comp.prune(kf[:, :Lc].contiguous(), self.sparsity)
+                    L.vs[:, :Lc] = comp.prune(vf[:, :Lc].contiguous(), self.sparsity)
+            del q, k, v, att
+        self.tokens, self.compressed, self.wlen = T, Lc, T - Lc
+        self._stage_hint = None
+        return self._logits(x[:, -1])
+
+    # ------------------------------------------------------------------ one decode step
+    def _hint(self):
+        if self._stage_hint is None:
+            self._stage_hint = max(max(L.ks.stage_hint(), L.vs.stage_hint()) for L in self.layers) if self.compressed else 8
+        return self._stage_hint
+
+    @torch.no_grad()
+    def decode_step(self, token: torch.Tensor) -> torch.Tensor:
+        """token [B] (ids of the newest position) -> logits [B, vocab]."""
+        B = self.B
+        pos = torch.tensor([self.tokens], device=self.dev)
+        x = self.embed[token].view(B, 1, -1)
+        hint = self._hint() if self.sparse else 0
+        w = self.wlen
+        for L in self.layers:
+            h = _rms(x, L.n1, self.s.rms_eps)
+            q, k, v = self._qkv(L, h, pos)
+            kf, vf = k.reshape(B * self.hkv, D), v.reshape(B * self.hkv, D)
+            if self.sparse:
+                L.kwin[:, w], L.vwin[:, w] = kf, vf
+                att = ops.decode_attention(q.reshape(B * self.hq, D), L.ks, L.vs, L.kwin[:, :w + 1], L.vwin[:, :w + 1],
+                                           self.G, stage_halves=hint)
+            else:
+                t = self.tokens
+                L.ks[:, t], L.vs[:, t] = kf, vf
+                kk = L.ks[:, :t + 1].float().repeat_interleave(self.G, dim=0)
+                vv = L.vs[:, :t + 1].float().repeat_interleave(self.G, dim=0)
+                sc = torch.bmm(kk, q.reshape(B * self.hq, D, 1).float()).squeeze(-1) / math.sqrt(D)
+                att = torch.bmm(torch.softmax(sc, -1).unsqueeze(1), vv).squeeze(1).half()
+            x = x + self._allreduce(F.linear(att.view(B, 1, self.hq * D), L.wo))
+            x = x + self._mlp(L, _rms(x, L.n2, self.s.rms_eps))
+        self.tokens += 1
+        self.wlen += 1
+        if self.wlen == self.wcap:
+            self._compress_oldest()
+        return self._logits(x[:, 0])
+
+    def _compress_oldest(self):
+        """The window reached residual + 256 tokens: its oldest 256 join the compressed cache."""
+        c = self.compressed
+        for L in self.layers:
+            if self.sparse:
+                L.ks.append(L.kwin[:, :256], self.rank_keep)
+                L.vs.append(L.vwin[:, :256], self.rank_keep)
+                L.kwin[:, :self.residual] = L.kwin[:, 256:].clone()
+                L.vwin[:, :self.residual] = L.vwin[:, 256:].clone()
+            else:
+                L.ks[:, c:c + 256] = comp.prune(L.ks[:, c:c + 256].contiguous(), self.sparsity)
+                L.vs[:, c:c + 256] = comp.prune(L.vs[:, c:c + 256].contiguous(), self.sparsity)
+        self.compressed += 256
+        self.wlen -= 256
+        self._stage_hint = None
+
+    @torch.no_grad()
+    def generate(self, tokens: torch.Tensor, steps: int):
+        """Greedy decoding; returns the generated ids [B, steps]."""
+        nxt = self.prefill(tokens).argmax(-1)
+        out = [nxt]
+        for _ in range(steps - 1):
+            nxt = self.decode_step(nxt).argmax(-1)
+            out.append(nxt)
+        return torch.stack(out, dim=1)
