@@ -168,6 +168,8 @@ int mfar_decode_plan(int n_kv_heads, int n_tokens, int window, int nsplit_hint, 
  * (key op, window matmul, softmax, value op, window matmul, add) in one call.
  * k_window/v_window: dense fp16 [n_kv_heads][window][128] with the given strides
  * (elements, multiples of 8); window may be 0.  workspace: mfar_decode_plan bytes.
+ * window_len_dev: NULL, or a device int32 holding the current window length (<= window, which is then the
+ * capacity): lets a launch captured in a CUDA graph be replayed while the window grows.
  * nsplit 0 = automatic.  flags: 0, or one of MFAR_DECODE_FORCE_* to pin the kernel variant
  * (64-token block kernel / 256-token superblock kernel) instead of the size heuristic. */
 int mfar_decode_attention_fp16(
@@ -177,8 +179,8 @@ int mfar_decode_attention_fp16(
     const int64_t* v_bitmaps, int64_t v_bmp_head_stride, const int32_t* v_accum, int64_t v_acc_head_stride,
     const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride,
     int n_tokens, const void* k_window, const void* v_window, int64_t win_head_stride, int64_t win_token_stride,
-    int window, float softmax_scale, void* out, int64_t out_stride, void* workspace, size_t workspace_bytes,
-    int nsplit, int stage_halves, int flags, uint32_t* dev_status, void* stream);
+    int window, const int32_t* window_len_dev, float softmax_scale, void* out, int64_t out_stride, void* workspace,
+    size_t workspace_bytes, int nsplit, int stage_halves, int flags, uint32_t* dev_status, void* stream);
 
 /* scores[i*scores_stride + t] = sum_c K~[i/group][t][c] * q[i][c]  (fp32 accumulate, fp16 store).
  * Replaces mustafar_key_formulation -> Key_SplitK_API -> Key_Kernel

@@ -95,7 +95,10 @@ __global__ void __launch_bounds__(kThreads, MFAR_MIN_BLOCKS) decode_kernel(Decod
     lane_byte_constants(kb, sel, mh, ml);
 
     const int blk0 = is_window ? 0 : split * p.bps;
-    int nb = is_window ? (p.W + 63) / 64 : min(p.bps, p.nblk - blk0);
+    // the window length may live in device memory (so that a captured launch can be replayed while
+    // the window grows); p.W is then only its upper bound
+    const int W = (is_window && p.W_dev) ? max(0, min(*p.W_dev, p.W)) : p.W;
+    int nb = is_window ? (W + 63) / 64 : min(p.bps, p.nblk - blk0);
     if (nb < 0) nb = 0;
 
     // ---- prologue: q to shared memory, block offsets of this split, barriers
@@ -234,7 +237,7 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
 #pragma unroll
                 for (int t = 0; t < 8; ++t) {
                     const int tok = i * 64 + kb * 8 + t;
-                    if (tok < p.W) {
+                    if (tok < W) {
                         const uint4 raw = ldg_nc_u4(p.kwin + h * p.win_hs + tok * p.win_ts + c0);
                         const __half2* hv = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
@@ -287,8 +290,8 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
                         s0 *= p.scale_log2;
                         s1 *= p.scale_log2;
                         if (is_window) {
-                            if (i * 64 + 2 * lane >= p.W) s0 = -INFINITY;
-                            if (i * 64 + 2 * lane + 1 >= p.W) s1 = -INFINITY;
+                            if (i * 64 + 2 * lane >= W) s0 = -INFINITY;
+                            if (i * 64 + 2 * lane + 1 >= W) s1 = -INFINITY;
                         }
                         const float m_new = fmaxf(m_run[j], warp_max_f32(fmaxf(s0, s1)));
                         const float a = fast_exp2(m_run[j] - m_new);   // exp2(-inf) = 0 on the first block
@@ -338,7 +341,7 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
                 for (int s = 0; s < 16 / 2; ++s) {
                     const int t = warp * 16 + s * 2 + par;
                     const int tok = i * 64 + t;
-                    if (tok < p.W) {
+                    if (tok < W) {
                         const uint4 raw = ldg_nc_u4(p.vwin + h * p.win_hs + tok * p.win_ts + half_id * 64 + kb * 8);
                         const __half2* hv = reinterpret_cast<const __half2*>(&raw);
                         float coef[G];
@@ -479,8 +482,8 @@ int launch_combine(const float* ws, int nrec, int G, int normalise, void* out, i
 }
 
 int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G, const void* kwin, const void* vwin,
-                         int64_t win_hs, int64_t win_ts, int W, float softmax_scale, float* ws, int rec_index,
-                         unsigned* dev_status, cudaStream_t s) {
+                         int64_t win_hs, int64_t win_ts, int W, const int* W_dev, float softmax_scale, float* ws,
+                         int rec_index, unsigned* dev_status, cudaStream_t s) {
     if (!kwin || !vwin) return MFAR_ERR_ARG;
     if ((reinterpret_cast<uintptr_t>(kwin) & 15) || (reinterpret_cast<uintptr_t>(vwin) & 15) || (win_hs & 7) || (win_ts & 7))
         return MFAR_ERR_ALIGN;
@@ -492,6 +495,7 @@ int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G,
     p.win_hs = win_hs;
     p.win_ts = win_ts;
     p.W = W;
+    p.W_dev = W_dev;
     p.nsplit = rec_index;
     p.split_offset = rec_index;
     p.cap = 8;
@@ -557,8 +561,8 @@ extern "C" int mfar_decode_attention_fp16(
     const int64_t* v_bitmaps, int64_t v_bmp_head_stride, const int32_t* v_accum, int64_t v_acc_head_stride,
     const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride,
     int n_tokens, const void* k_window, const void* v_window, int64_t win_head_stride, int64_t win_token_stride,
-    int window, float softmax_scale, void* out, int64_t out_stride, void* workspace, size_t workspace_bytes,
-    int nsplit, int stage_halves, int flags, uint32_t* dev_status, void* stream) {
+    int window, const int32_t* window_len_dev, float softmax_scale, void* out, int64_t out_stride, void* workspace,
+    size_t workspace_bytes, int nsplit, int stage_halves, int flags, uint32_t* dev_status, void* stream) {
     if (n_kv_heads <= 0 || group <= 0 || n_tokens < 0 || (n_tokens % 64) || window < 0) return MFAR_ERR_ARG;
     if (n_tokens == 0 && window == 0) return MFAR_ERR_ARG;
     if (group != 1 && group != 2 && group != 4 && group != 8) return MFAR_ERR_ARG;
@@ -591,6 +595,7 @@ extern "C" int mfar_decode_attention_fp16(
     p.win_hs = win_head_stride;
     p.win_ts = win_token_stride;
     p.W = window;
+    p.W_dev = window_len_dev;
     p.nblk = n_tokens / 64;
     p.cap = pick_cap(stage_halves);
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
@@ -620,7 +625,7 @@ extern "C" int mfar_decode_attention_fp16(
         if (r) return r;
         if (window > 0) {
             r = launch_window_record(q, q_stride, n_kv_heads, group, k_window, v_window, win_head_stride,
-                                     win_token_stride, window, softmax_scale, p.ws, ns, dev_status, s);
+                                     win_token_stride, window, window_len_dev, softmax_scale, p.ws, ns, dev_status, s);
             if (r) return r;
         }
     } else if (use_sb) {

@@ -146,6 +146,7 @@ struct DecodeParams {
     const __half* vwin;
     int64_t win_hs, win_ts;
     int W;
+    const int* W_dev;      // optional: window length in device memory (then W is its upper bound)
     int nblk, nsplit, bps; // compressed blocks, splits over them, blocks per split
     int cap;               // halves of packed values a stage can hold per tensor
     float scale_log2;      // softmax scale * log2(e)
@@ -170,7 +171,7 @@ int launch_combine(const float* ws, int nrec, int G, int normalise, void* out, i
                    cudaStream_t s);
 // dense recent-token window as split record `rec_index` of a workspace with rec_index + 1 records per kv head
 int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G, const void* kwin, const void* vwin,
-                         int64_t win_hs, int64_t win_ts, int W, float softmax_scale, float* ws, int rec_index,
-                         unsigned* dev_status, cudaStream_t s);
+                         int64_t win_hs, int64_t win_ts, int W, const int* W_dev, float softmax_scale, float* ws,
+                         int rec_index, unsigned* dev_status, cudaStream_t s);
 
 }  // namespace mfar

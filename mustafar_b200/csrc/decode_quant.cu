@@ -500,7 +500,7 @@ extern "C" int mfar_decode_attention_quant(
     }
     if (window > 0) {
         r = launch_window_record(q, q_stride, n_kv_heads, group, k_window, v_window, win_head_stride, win_token_stride,
-                                 window, softmax_scale, p.ws, p.nsplit, dev_status, s);
+                                 window, nullptr, softmax_scale, p.ws, p.nsplit, dev_status, s);
         if (r) return r;
     }
     return launch_combine(p.ws, p.nrec, group, 1, out, out_stride, n_kv_heads * group, s);

@@ -29,6 +29,7 @@ def main():
     ap.add_argument("--parallel", default="dp", choices=["tp", "dp"])
     ap.add_argument("--sparsity", type=float, default=0.7)
     ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--no-graph", action="store_true", help="launch every decode step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--dense", action="store_true", help="dense pruned cache + torch attention (comparison arm)")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
@@ -58,7 +59,7 @@ def main():
     nxt = model.prefill(toks).argmax(-1)
     e[1].record()
     for _ in range(a.new - 1):
-        nxt = model.decode_step(nxt).argmax(-1)
+        nxt = model.decode_step(nxt, graph=not a.no_graph).argmax(-1)
     e[2].record()
     torch.cuda.synchronize()
     prefill_ms = max_over_ranks(e[0].elapsed_time(e[1]), dist, dev)
@@ -70,7 +71,8 @@ def main():
             "value": seqs * (a.new - 1) / (decode_ms * 1e-3), "tpot_ms": decode_ms / (a.new - 1), "ttft_ms": prefill_ms,
             "config": {"workload": f"Llama-3-8B shape, {a.layers} layers, prompt {a.prompt}, {a.new} new tokens, "
                                    f"batch {a.batch} per {'job' if tp > 1 else 'GPU'}, sparsity {a.sparsity}, window 128",
-                       "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}", "cache": "dense-pruned torch" if a.dense else "sparse fp16"},
+                       "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}", "cache": "dense-pruned torch" if a.dense else "sparse fp16",
+                       "cuda_graph": bool(not a.no_graph and not a.dense)},
             "data": "synthetic (random-init weights, random prompt ids)", "dtype": "f16"}))
     if dist is not None:
         dist.barrier()

@@ -121,6 +121,8 @@ class SparseLlama:
                 L.kwin = L.vwin = None
             self.layers.append(L)
         self._stage_hint = None
+        self._graph = None
+        self._eager_done = False
 
     # ------------------------------------------------------------------ pieces
     def _allreduce(self, x):
@@ -183,19 +185,25 @@ class SparseLlama:
             self._stage_hint = max(max(L.ks.stage_hint(), L.vs.stage_hint()) for L in self.layers) if self.compressed else 8
         return self._stage_hint
 
-    @torch.no_grad()
-    def decode_step(self, token: torch.Tensor) -> torch.Tensor:
-        """token [B] (ids of the newest position) -> logits [B, vocab]."""
+    def _step_body(self, token: torch.Tensor, dev_state: bool) -> torch.Tensor:
+        """One decode step for token ids [B].  With dev_state the position and the window length are
+        read from device tensors (and advanced on the device), so the launch sequence can be captured
+        in a CUDA graph and replayed; otherwise they are the host counters."""
         B = self.B
-        pos = torch.tensor([self.tokens], device=self.dev)
         x = self.embed[token].view(B, 1, -1)
         hint = self._hint() if self.sparse else 0
         w = self.wlen
+        pos = self._pos_dev if dev_state else torch.tensor([self.tokens], device=self.dev)
         for L in self.layers:
             h = _rms(x, L.n1, self.s.rms_eps)
             q, k, v = self._qkv(L, h, pos)
             kf, vf = k.reshape(B * self.hkv, D), v.reshape(B * self.hkv, D)
-            if self.sparse:
+            if self.sparse and dev_state:
+                L.kwin.index_copy_(1, self._widx_dev, kf.unsqueeze(1))
+                L.vwin.index_copy_(1, self._widx_dev, vf.unsqueeze(1))
+                att = ops.decode_attention(q.reshape(B * self.hq, D), L.ks, L.vs, L.kwin, L.vwin, self.G,
+                                           stage_halves=hint, window_len=self._wlen_dev)
+            elif self.sparse:
                 L.kwin[:, w], L.vwin[:, w] = kf, vf
                 att = ops.decode_attention(q.reshape(B * self.hq, D), L.ks, L.vs, L.kwin[:, :w + 1], L.vwin[:, :w + 1],
                                            self.G, stage_halves=hint)
@@ -208,11 +216,51 @@ class SparseLlama:
                 att = torch.bmm(torch.softmax(sc, -1).unsqueeze(1), vv).squeeze(1).half()
             x = x + self._allreduce(F.linear(att.view(B, 1, self.hq * D), L.wo))
             x = x + self._mlp(L, _rms(x, L.n2, self.s.rms_eps))
+        if dev_state:
+            self._pos_dev += 1
+            self._widx_dev += 1
+            self._wlen_dev += 1
+        return self._logits(x[:, 0])
+
+    def _advance(self):
         self.tokens += 1
         self.wlen += 1
         if self.wlen == self.wcap:
             self._compress_oldest()
-        return self._logits(x[:, 0])
+            self._graph = None
+
+    @torch.no_grad()
+    def decode_step(self, token: torch.Tensor, graph: bool = False) -> torch.Tensor:
+        """token [B] (ids of the newest position) -> logits [B, vocab].
+
+        graph=True replays a CUDA graph of the step (re-captured after every 256-token block append,
+        because the compressed length is a launch argument); the first step of each epoch runs eagerly."""
+        if not (graph and self.sparse):
+            out = self._step_body(token, False)
+            self._advance()
+            return out
+        if self._graph is None:
+            if not self._eager_done:
+                self._eager_done = True
+                out = self._step_body(token, False)       # sizes workspaces, resolves the stage hint
+                self._advance()
+                return out
+            self._pos_dev = torch.tensor([self.tokens], device=self.dev)
+            self._widx_dev = torch.tensor([self.wlen], device=self.dev)
+            self._wlen_dev = torch.tensor([self.wlen + 1], device=self.dev, dtype=torch.int32)
+            self._tok_buf = token.clone()
+            self._hint()
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._logits_buf = self._step_body(self._tok_buf, True)
+            self._graph = g
+        self._tok_buf.copy_(token)
+        self._graph.replay()
+        out = self._logits_buf
+        self._eager_done = False if self.wlen + 1 == self.wcap else self._eager_done
+        self._advance()
+        return out
 
     def _compress_oldest(self):
         """The window reached residual + 256 tokens: its oldest 256 join the compressed cache."""
@@ -231,11 +279,11 @@ class SparseLlama:
         self._stage_hint = None
 
     @torch.no_grad()
-    def generate(self, tokens: torch.Tensor, steps: int):
+    def generate(self, tokens: torch.Tensor, steps: int, graph: bool = False):
         """Greedy decoding; returns the generated ids [B, steps]."""
         nxt = self.prefill(tokens).argmax(-1)
         out = [nxt]
         for _ in range(steps - 1):
-            nxt = self.decode_step(nxt).argmax(-1)
+            nxt = self.decode_step(nxt, graph).argmax(-1)
             out.append(nxt)
         return torch.stack(out, dim=1)

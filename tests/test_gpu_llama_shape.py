@@ -32,6 +32,22 @@ def test_sparse_model_matches_dense_pruned_model():
         L.ks.check(); L.vs.check()
 
 
+def test_graph_replay_matches_eager_steps():
+    """Replaying the captured step (device-resident position / window length) gives the eager logits,
+    across a block append that forces a re-capture."""
+    from mustafar_b200.llama_shape import SparseLlama, tiny_shape
+    shape, B, prompt = tiny_shape(), 2, 256 + 128 + 240
+    kw = dict(batch=B, max_tokens=1024, device="cuda", seed=5)
+    a, b = SparseLlama(shape, **kw), SparseLlama(shape, **kw)
+    toks = torch.randint(0, shape.vocab, (B, prompt), device="cuda", generator=torch.Generator(device="cuda").manual_seed(4))
+    la, lb = a.prefill(toks), b.prefill(toks)
+    for i in range(40):
+        nxt = la.argmax(-1)
+        la, lb = a.decode_step(nxt), b.decode_step(nxt, graph=True).clone()
+        assert oracle.rel_l2(lb.float().cpu(), la.float().cpu()) < 1e-3, i
+    assert a.compressed == b.compressed == 512 and a.wlen == b.wlen
+
+
 def test_generate_runs_and_is_deterministic():
     from mustafar_b200.llama_shape import SparseLlama, tiny_shape
     shape = tiny_shape()

@@ -1,0 +1,40 @@
+"""Worker of test_gpu_tensor_parallel.py (launched by torch.distributed.run, one rank per GPU):
+the head-tensor-parallel model must reproduce the single-GPU logits."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from mustafar_b200.llama_shape import SparseLlama, tiny_shape  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    shape, B, prompt = tiny_shape(), 2, 256 + 128 + 100
+    toks = torch.randint(0, shape.vocab, (B, prompt), device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
+    tp = SparseLlama(shape, B, 1024, "cuda", seed=11, tp_rank=rank, tp_world=world, dist=dist)
+    lt = tp.prefill(toks)
+    ref = SparseLlama(shape, B, 1024, "cuda", seed=11) if rank == 0 else None
+    lr = ref.prefill(toks) if rank == 0 else None
+    worst = 0.0
+    for i in range(12):
+        nxt = lt.argmax(-1)
+        dist.broadcast(nxt, 0)
+        lt = tp.decode_step(nxt, graph=(i >= 6))
+        if rank == 0:
+            lr = ref.decode_step(nxt)
+            err = float(torch.linalg.norm(lt.float() - lr.float()) / torch.linalg.norm(lr.float()))
+            worst = max(worst, err)
+    if rank == 0:
+        print("TP_WORST_REL_L2", worst, flush=True)
+        assert worst < 5e-3, worst
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
