@@ -235,7 +235,7 @@ class SparseLlama:
 
         graph=True replays a CUDA graph of the step (re-captured after every 256-token block append,
         because the compressed length is a launch argument); the first step of each epoch runs eagerly."""
-        if not (graph and self.sparse):
+        if not (graph and self.sparse and self.tp_world == 1):    # NCCL collectives stay outside graph capture
             out = self._step_body(token, False)
             self._advance()
             return out

@@ -16,6 +16,6 @@ def test_tp2_matches_single_gpu():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", "29661", os.path.join(HERE, "tp_worker.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900, env=env)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
     assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
     assert "TP_WORST_REL_L2" in r.stdout

@@ -24,7 +24,7 @@ def main():
     for i in range(12):
         nxt = lt.argmax(-1)
         dist.broadcast(nxt, 0)
-        lt = tp.decode_step(nxt, graph=(i >= 6))
+        lt = tp.decode_step(nxt)          # eager: collectives are not captured in CUDA graphs here
         if rank == 0:
             lr = ref.decode_step(nxt)
             err = float(torch.linalg.norm(lt.float() - lr.float()) / torch.linalg.norm(lr.float()))
