@@ -26,7 +26,13 @@ namespace mfar {
 
 constexpr int kStWarps = 4;                 // consumer warps
 constexpr int kStThreads = kStWarps * 32;
-constexpr int kStStages = 2;
+#ifndef MFAR_ST_STAGES
+#define MFAR_ST_STAGES 2
+#endif
+#ifndef MFAR_ST_MINB
+#define MFAR_ST_MINB 4
+#endif
+constexpr int kStStages = MFAR_ST_STAGES;
 constexpr int kStMaxBlocks = 512;
 
 __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
@@ -90,7 +96,7 @@ struct StLayout {
         stage = s_vval + val;
         size_t o = 0;
         stages = o; o += kStStages * stage;
-        bars = o;   o += 64;
+        bars = o;   o += 32 * kStStages;   // full + ready barriers and the done counter of every stage
         q = o;      o += kD * G * sizeof(coef_t);
         red = o;    o += static_cast<size_t>(kStWarps) * 32 * ROW * 4;     // reused by the epilogue
         ps = o;     o += kStWarps * 16 * G * sizeof(coef_t) + 64;
@@ -102,7 +108,7 @@ struct StLayout {
 };
 
 template <int G, bool MIXED>
-__global__ void __launch_bounds__(kStThreads, 4) decode_stream_kernel(DecodeParams p) {
+__global__ void __launch_bounds__(kStThreads, MFAR_ST_MINB) decode_stream_kernel(DecodeParams p) {
     using L = StLayout<G, MIXED>;
     using coef_t = typename L::coef_t;
     constexpr int ROW = L::ROW;
@@ -114,6 +120,7 @@ __global__ void __launch_bounds__(kStThreads, 4) decode_stream_kernel(DecodePara
     unsigned long long* bar_full = bars;                 // [kStStages] bulk copies landed
     unsigned long long* bar_ready = bars + kStStages;    // [kStStages] ... and offsets converted
     unsigned* done_cnt = reinterpret_cast<unsigned*>(bars + 2 * kStStages);   // [kStStages] warps done with the stage
+    static_assert(2 * kStStages * 8 + kStStages * 4 <= 32 * kStStages, "barrier area");
     coef_t* qs = reinterpret_cast<coef_t*>(smem + lay.q);           // [128][G]
     float* red = reinterpret_cast<float*>(smem + lay.red);          // [warp][lane][ROW]
     coef_t* ps = reinterpret_cast<coef_t*>(smem + lay.ps);          // [warp][16][G]

@@ -22,7 +22,9 @@ _status: dict = {}
 
 
 def _debug_check() -> bool:
-    return os.environ.get("MUSTAFAR_B200_CHECK", "0") == "1"
+    """MUSTAFAR_B200_CHECK=1: synchronise after every op and raise on device-reported errors
+    (never while the stream is being captured into a CUDA graph, where a sync is illegal)."""
+    return os.environ.get("MUSTAFAR_B200_CHECK", "0") == "1" and not torch.cuda.is_current_stream_capturing()
 
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
