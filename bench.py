@@ -46,7 +46,7 @@ def parse():
     ap.add_argument("--sparsity", type=float, default=0.7)
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--variant", default="auto", choices=["auto", "block", "superblock", "stream", "stream16"])
+    ap.add_argument("--variant", default="auto", choices=["auto", "block", "block32", "superblock", "stream", "stream16"])
     return ap.parse_args()
 
 

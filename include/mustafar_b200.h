@@ -46,7 +46,9 @@ typedef enum {
 
 enum { MFAR_KIND_KEY = 0, MFAR_KIND_VALUE = 1 };
 enum { MFAR_DECODE_FORCE_BLOCK = 1, MFAR_DECODE_FORCE_SUPERBLOCK = 2, MFAR_DECODE_FORCE_STREAM = 4,
-       MFAR_DECODE_FP16_COEF = 8 /* stream kernel: q and the probabilities enter the FMA as fp16 */ };
+       MFAR_DECODE_FP16_COEF = 8 /* stream kernel: q and the probabilities enter the FMA as fp16 */,
+       MFAR_DECODE_FP32_COEF = 16 /* block kernel: keep the probabilities in fp32 (default: rounded to fp16
+                                     before P.V, as the reference model does, one mixed-precision FMA per value) */ };
 
 int mfar_version(void);
 const char* mfar_status_string(int status);

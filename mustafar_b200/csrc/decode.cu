@@ -19,6 +19,8 @@
 // K phase: lane owns 8 tokens, loops over its warp's 32 channels (a K tile is one
 // channel x 64 tokens).  V phase: lane owns 8 channels, loops over its warp's 16
 // tokens (a V tile is one token x 64 channels).  Tensor cores are not used.
+#include <type_traits>
+
 #include "decode_common.cuh"
 
 namespace mfar {
@@ -69,17 +71,29 @@ struct SmemLayout {
 #ifndef MFAR_STEP_UNROLL
 #define MFAR_STEP_UNROLL 8
 #endif
+// Ablation switches for timing experiments (never set in a product build: results are then wrong):
+//   MFAR_ABL_NOLOAD     only the first kStages blocks are fetched, later iterations reuse the stages
+//   MFAR_ABL_NOSOFTMAX  skip the scores -> probabilities section
+//   MFAR_ABL_NOSYNC     CTA barriers inside the block loop become warp barriers
+#ifdef MFAR_ABL_NOSYNC
+#define MFAR_LOOP_SYNC() __syncwarp()
+#else
+#define MFAR_LOOP_SYNC() __syncthreads()
+#endif
 #define MFAR_PRAGMA(x) _Pragma(#x)
 #define MFAR_UNROLL(n) MFAR_PRAGMA(unroll n)
 
-template <int G, int MODE>
+template <int G, int MODE, bool MIXED>
 __global__ void __launch_bounds__(kThreads, MFAR_MIN_BLOCKS) decode_kernel(DecodeParams p) {
+    // MIXED: q and the probabilities are held as fp16 and multiplied by the packed halves in one
+    // mixed-precision FMA (exact for KEY / VALUE, whose coefficients are fp16 inputs anyway)
+    using coef_t = typename std::conditional<MIXED, unsigned short, float>::type;
     extern __shared__ __align__(128) unsigned char smem[];
     const SmemLayout<G, MODE> lay(p.cap);
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + lay.bars);
-    float* qs = reinterpret_cast<float*>(smem + lay.qs);          // [128][G]
+    coef_t* qs = reinterpret_cast<coef_t*>(smem + lay.qs);        // [128][G]
     float* spart = reinterpret_cast<float*>(smem + lay.spart);    // [plane][G][64]
-    float* ps = reinterpret_cast<float*>(smem + lay.ps);          // [64][G]
+    coef_t* ps = reinterpret_cast<coef_t*>(smem + lay.ps);        // [64][G]
     float* alpha_s = reinterpret_cast<float*>(smem + lay.alpha);  // [G]
     unsigned* koff = reinterpret_cast<unsigned*>(smem + lay.koff);  // [2][128] halves, relative to the block
     unsigned* voff = reinterpret_cast<unsigned*>(smem + lay.voff);
@@ -105,7 +119,7 @@ __global__ void __launch_bounds__(kThreads, MFAR_MIN_BLOCKS) decode_kernel(Decod
     if (MODE != MODE_VALUE) {
         for (int i = tid; i < kD * G; i += kThreads) {
             const int c = i / G, g = i % G;
-            qs[i] = __half2float(p.q[(static_cast<int64_t>(h) * G + g) * p.q_stride + c]);
+            store_coef(&qs[i], __half2float(p.q[(static_cast<int64_t>(h) * G + g) * p.q_stride + c]));
         }
     }
     const int* kacc = p.k.acc + h * p.k.acc_hs;
@@ -206,13 +220,25 @@ __global__ void __launch_bounds__(kThreads, MFAR_MIN_BLOCKS) decode_kernel(Decod
         const unsigned* vo = voff + (i & 1) * 128;
 
         if (!is_window) {
+#ifdef MFAR_ABL_NOLOAD
+            if (i < kStages && !mbar_wait(&bars[i % kStages], 0)) timed_out = true;
+#else
             if (i + 1 < nb) fetch_offsets(i + 1);
             if (!mbar_wait(&bars[i % kStages], (i / kStages) & 1)) timed_out = true;
+#endif
         }
+#ifdef MFAR_ABL_NOSYNC
+        if (timed_out) break;
+#else
         if (__syncthreads_or(timed_out)) { timed_out = true; break; }   // also publishes the stage hand-off below
+#endif
         // every warp is done with block i-1, so its stage (untouched so far when i == 0) can
         // take block i + kStages - 1
+#ifdef MFAR_ABL_NOLOAD
+        if (!is_window && tid == 0 && i == 0 && kStages - 1 < nb) issue(kStages - 1);
+#else
         if (!is_window && tid == 0 && i + kStages - 1 < nb) issue(i + kStages - 1);
+#endif
 
         // ------------------------------------------------------------ K phase
         if (MODE != MODE_VALUE) {
@@ -226,7 +252,7 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
                 for (int s = 0; s < 32 / 4; ++s) {
                     const int c = warp * 32 + s * 4 + gi;
                     const uint2 bm = kbm[c];
-                    float coef[G];
+                    coef_t coef[G];
                     load_coef<G>(qs + c * G, coef);
                     tile_step<G>(bm.y, bm.x, kval + ko[c], sel, mh, ml, coef, acc_s);
                 }
@@ -245,8 +271,8 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
                             const float2 f = __half22float2(hv[e]);
 #pragma unroll
                             for (int g = 0; g < G; ++g) {
-                                acc_s[t][g] = fmaf(f.x, qs[(c0 + 2 * e) * G + g], acc_s[t][g]);
-                                acc_s[t][g] = fmaf(f.y, qs[(c0 + 2 * e + 1) * G + g], acc_s[t][g]);
+                                acc_s[t][g] = fmaf(f.x, coef_to_float(qs[(c0 + 2 * e) * G + g]), acc_s[t][g]);
+                                acc_s[t][g] = fmaf(f.y, coef_to_float(qs[(c0 + 2 * e + 1) * G + g]), acc_s[t][g]);
                             }
                         }
                     }
@@ -260,18 +286,26 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
                 *reinterpret_cast<float4*>(dst + g * 64 + 4) = make_float4(acc_s[4][g], acc_s[5][g], acc_s[6][g], acc_s[7][g]);
             }
         }
-        if (MODE != MODE_VALUE) __syncthreads();
+        if (MODE != MODE_VALUE) MFAR_LOOP_SYNC();
 
         // ------------------------------------------------------------ scores -> probabilities
+#ifdef MFAR_ABL_NOSOFTMAX
+        if (false) {
+#else
         if (MODE == MODE_VALUE) {
+#endif
             // p comes from the caller: warp j loads heads j, j+4, ...; lane takes tokens 2*lane, 2*lane+1
             for (int g = warp; g < G; g += kWarps) {
                 const __half2 pv = *reinterpret_cast<const __half2*>(
                     p.p_in + (static_cast<int64_t>(h) * G + g) * p.p_stride + static_cast<int64_t>(blk0 + i) * 64 + 2 * lane);
-                ps[(2 * lane) * G + g] = __low2float(pv);
-                ps[(2 * lane + 1) * G + g] = __high2float(pv);
+                store_coef(&ps[(2 * lane) * G + g], __low2float(pv));
+                store_coef(&ps[(2 * lane + 1) * G + g], __high2float(pv));
             }
+#ifdef MFAR_ABL_NOSOFTMAX
+        } else if (false) {
+#else
         } else {
+#endif
 #pragma unroll
             for (int j = 0; j < kHeadsPerWarp; ++j) {
                 const int g = warp + j * kWarps;
@@ -295,19 +329,23 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
                         }
                         const float m_new = fmaxf(m_run[j], warp_max_f32(fmaxf(s0, s1)));
                         const float a = fast_exp2(m_run[j] - m_new);   // exp2(-inf) = 0 on the first block
-                        const float p0 = fast_exp2(s0 - m_new), p1 = fast_exp2(s1 - m_new);
+                        const float p0 = round_like(ps, fast_exp2(s0 - m_new)), p1 = round_like(ps, fast_exp2(s1 - m_new));
                         l_run[j] = l_run[j] * a + (p0 + p1);
                         m_run[j] = m_new;
-                        ps[(2 * lane) * G + g] = p0;
-                        ps[(2 * lane + 1) * G + g] = p1;
+                        store_coef(&ps[(2 * lane) * G + g], p0);
+                        store_coef(&ps[(2 * lane + 1) * G + g], p1);
                         if (lane == 0) alpha_s[g] = a;
                     }
                 }
             }
         }
         if (MODE != MODE_KEY) {
+#ifndef MFAR_ABL_NOLOAD
             if (!is_window && i + 1 < nb) store_offsets(i + 1);
-            __syncthreads();
+#else
+            if (!is_window && i + 1 < kStages) store_offsets(i + 1);
+#endif
+            MFAR_LOOP_SYNC();
         } else {
             if (i + 1 < nb) store_offsets(i + 1);
         }
@@ -333,7 +371,7 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
                     const int t = warp * 16 + s * 2 + par;
                     const int tile = half_id * 64 + t;
                     const uint2 bm = vbm[tile];
-                    float coef[G];
+                    coef_t coef[G];
                     load_coef<G>(ps + t * G, coef);
                     tile_step<G>(bm.y, bm.x, vval + vo[tile], sel, mh, ml, coef, acc_o);
                 }
@@ -344,8 +382,11 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
                     if (tok < W) {
                         const uint4 raw = ldg_nc_u4(p.vwin + h * p.win_hs + tok * p.win_ts + half_id * 64 + kb * 8);
                         const __half2* hv = reinterpret_cast<const __half2*>(&raw);
+                        coef_t craw[G];
+                        load_coef<G>(ps + t * G, craw);
                         float coef[G];
-                        load_coef<G>(ps + t * G, coef);
+#pragma unroll
+                        for (int g = 0; g < G; ++g) coef[g] = coef_to_float(craw[g]);
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
                             const float2 f = __half22float2(hv[e]);
@@ -412,28 +453,58 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
 // (normalise = 1) or the plain sum of O_s (normalise = 0).  One CTA per q head, 128 threads.
 __global__ void __launch_bounds__(128) combine_kernel(const float* ws, int nrec, int G, int normalise,
                                                       __half* out, int64_t out_stride) {
+    // weight of each record, computed once per CTA (records in chunks of 128), then every thread sums
+    // its channel over the records with independent, unrolled loads
+    __shared__ float w_s[128];
+    __shared__ float red_s[8];
     const int bq = blockIdx.x, h = bq / G, g = bq % G, c = threadIdx.x;
     const float* base = ws + ((static_cast<int64_t>(h) * nrec) * G + g) * kPartialStride;
     const int64_t step = static_cast<int64_t>(G) * kPartialStride;
     float M = -INFINITY;
-    if (normalise)
-        for (int s = 0; s < nrec; ++s) M = fmaxf(M, base[s * step + kPartM]);
+    if (normalise) {
+        for (int s = c; s < nrec; s += 128) M = fmaxf(M, base[s * step + kPartM]);
+#pragma unroll
+        for (int d = 16; d; d >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, d));
+        if ((c & 31) == 0) red_s[c >> 5] = M;
+        __syncthreads();
+        M = fmaxf(fmaxf(red_s[0], red_s[1]), fmaxf(red_s[2], red_s[3]));
+    }
     float o = 0.f, l = 0.f;
-    for (int s = 0; s < nrec; ++s) {
-        float w = 1.f;
-        if (normalise) {
-            const float ms = base[s * step + kPartM];
-            w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
-            l += w * base[s * step + kPartL];
+    for (int s0 = 0; s0 < nrec; s0 += 128) {
+        const int n = min(128, nrec - s0);
+        float wl = 0.f;
+        if (c < n) {
+            float w = 1.f;
+            if (normalise) {
+                const float ms = base[(s0 + c) * step + kPartM];
+                w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
+                wl = w * base[(s0 + c) * step + kPartL];
+            }
+            w_s[c] = w;
         }
-        o += w * base[s * step + c];
+#pragma unroll
+        for (int d = 16; d; d >>= 1) wl += __shfl_xor_sync(0xffffffffu, wl, d);
+        __syncthreads();                       // w_s written; red_s (max) consumed by everyone
+        if ((c & 31) == 0) red_s[4 + (c >> 5)] = wl;
+        const float* rec = base + s0 * step + c;
+        int s = 0;
+        for (; s + 8 <= n; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = rec[(s + u) * step];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) o += w_s[s + u] * v[u];
+        }
+        for (; s < n; ++s) o += w_s[s] * rec[s * step];
+        __syncthreads();                       // partial l sums written; w_s free for the next chunk
+        l += red_s[4] + red_s[5] + red_s[6] + red_s[7];
     }
     if (normalise) o = (l > 0.f) ? o / l : 0.f;
     out[bq * out_stride + c] = __float2half_rn(o);
 }
 
 // ---------------------------------------------------------------------------- host side
-template <int G, int MODE>
+template <int G, int MODE, bool MIXED>
 static int launch_decode(const DecodeParams& p, int n_kv_heads, int grid_x, cudaStream_t s) {
     const SmemLayout<G, MODE> lay(p.cap);
     // largest dynamic shared memory size opted into so far, per device (and per instantiation)
@@ -441,24 +512,31 @@ static int launch_decode(const DecodeParams& p, int n_kv_heads, int grid_x, cuda
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MFAR_ERR_LAUNCH;
     if (lay.total > configured[dev]) {
-        if (cudaFuncSetAttribute(decode_kernel<G, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(decode_kernel<G, MODE, MIXED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(lay.total)) != cudaSuccess)
             return MFAR_ERR_LAUNCH;
         configured[dev] = lay.total;
     }
-    decode_kernel<G, MODE><<<dim3(grid_x, n_kv_heads), kThreads, lay.total, s>>>(p);
+    decode_kernel<G, MODE, MIXED><<<dim3(grid_x, n_kv_heads), kThreads, lay.total, s>>>(p);
     return launch_status();
 }
 
+// fp32_coef: keep q / the probabilities in fp32 (ATTN only; KEY and VALUE take fp16 coefficients as
+// inputs, so the fp16 path is exact for them and always used)
 template <int MODE>
-static int dispatch_decode(const DecodeParams& p, int G, int n_kv_heads, int grid_x, cudaStream_t s) {
+static int dispatch_decode(const DecodeParams& p, int G, int n_kv_heads, int grid_x, cudaStream_t s, bool fp32_coef = false) {
+#define MFAR_BLK(GG)                                                                      \
+    case GG:                                                                              \
+        if (MODE == MODE_ATTN && fp32_coef) return launch_decode<GG, MODE, false>(p, n_kv_heads, grid_x, s); \
+        return launch_decode<GG, MODE, true>(p, n_kv_heads, grid_x, s);
     switch (G) {
-        case 1: return launch_decode<1, MODE>(p, n_kv_heads, grid_x, s);
-        case 2: return launch_decode<2, MODE>(p, n_kv_heads, grid_x, s);
-        case 4: return launch_decode<4, MODE>(p, n_kv_heads, grid_x, s);
-        case 8: return launch_decode<8, MODE>(p, n_kv_heads, grid_x, s);
+        MFAR_BLK(1)
+        MFAR_BLK(2)
+        MFAR_BLK(4)
+        MFAR_BLK(8)
         default: return MFAR_ERR_ARG;
     }
+#undef MFAR_BLK
 }
 
 static int pick_cap(int stage_halves) {
@@ -521,17 +599,37 @@ static void sb_split(int n_kv_heads, int nblk, int hint, int* ns_out, int* sps_o
     *ns_out = (nsb + sps - 1) / sps;
 }
 
+// Split count of the block kernel.  The grid is n_kv_heads * ns CTAs of bps = ceil(nblk / ns) blocks.
+// The cost of a candidate follows a model fitted to a measured sweep of ns over batch 1..64 and
+// 4k..32k tokens on a B200 (all times in units of one block on an otherwise idle SM, ~2 us):
+//   * a CTA costs w = bps + 1.1 (prologue, partial record);
+//   * x = CTAs / 148 is the load per SM; an SM's throughput with o = min(x, 4) resident CTAs is
+//     rate(o) = 1 / 2 / 2.76 / 2.13 at o = 1 / 2 / 3 / 4, linear in between (the dip at 4 is the fit's
+//     way of saying that a grid which fits in one not-quite-full wave beats one that needs two);
+//   * the last, partly filled wave costs another 0.8 w once the SMs hold more than one CTA;
+//   * the combine kernel adds 0.035 per record.
+// The pick stays within 2 % of the best swept ns on every measured shape.
 static int block_split(int n_kv_heads, int nblk, int hint) {
     if (nblk <= 0) return 0;
     const int min_ns = (nblk + kMaxBlocksPerSplit - 1) / kMaxBlocksPerSplit;
-    int ns;
-    if (hint > 0) {
-        ns = hint;
-    } else {
-        // ~4 CTAs per SM over 148 SMs, at least 2 blocks per split
-        ns = (148 * 4 + n_kv_heads - 1) / n_kv_heads;
-        const int max_ns = (nblk + 1) / 2;
-        if (ns > max_ns) ns = max_ns;
+    int ns = hint;
+    if (hint <= 0) {
+        double best = -1.0;
+        const int max_ns = nblk < 128 ? nblk : 128;
+        for (int cand = min_ns > 0 ? min_ns : 1; cand <= max_ns; ++cand) {
+            const int bps = (nblk + cand - 1) / cand;
+            const int real = (nblk + bps - 1) / bps;
+            const double x = static_cast<double>(n_kv_heads) * real / 148.0;
+            const double w = bps + 1.1;
+            double cost = w;
+            if (x > 1.0) {
+                const double o = x < 4.0 ? x : 4.0;
+                const double rate = o < 2.0 ? o : (o < 3.0 ? 2.0 + 0.76 * (o - 2.0) : 2.76 - 0.63 * (o - 3.0));
+                cost = x * w / rate + 0.8 * w * (x - 1.0 < 1.0 ? x - 1.0 : 1.0);
+            }
+            cost += 0.035 * real;
+            if (best < 0 || cost < best) { best = cost; ns = real; }
+        }
     }
     if (ns < min_ns) ns = min_ns;
     if (ns > nblk) ns = nblk;
@@ -647,7 +745,7 @@ extern "C" int mfar_decode_attention_fp16(
         p.nsplit = ns;
         p.bps = ns > 0 ? (p.nblk + ns - 1) / ns : 0;
         nrec = ns + (window > 0 ? 1 : 0);
-        r = dispatch_decode<MODE_ATTN>(p, group, n_kv_heads, nrec, s);
+        r = dispatch_decode<MODE_ATTN>(p, group, n_kv_heads, nrec, s, (flags & MFAR_DECODE_FP32_COEF) != 0);
         if (r) return r;
     }
     combine_kernel<<<n_kv_heads * group, 128, 0, s>>>(p.ws, nrec, group, 1, static_cast<__half*>(out), out_stride);

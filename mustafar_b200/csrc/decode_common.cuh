@@ -121,6 +121,55 @@ __device__ __forceinline__ void load_coef(const float* p, float (&c)[G]) {
     }
 }
 
+__device__ __forceinline__ float fma_h(float acc, unsigned short a, unsigned short b) {
+    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc) : "h"(a), "h"(b));
+    return acc;
+}
+
+// fp16-coefficient tile step: the packed half and the coefficient go straight into one mixed-precision
+// FMA (fp16 x fp16 + fp32, full rate on sm_100), which saves the fp16 -> fp32 conversion of every value.
+template <int G>
+__device__ __forceinline__ void tile_step(unsigned hi, unsigned lo, const unsigned short* vals, unsigned sel,
+                                          unsigned mh, unsigned ml, const unsigned short (&coef)[G], float (&acc)[8][G]) {
+    const unsigned byte = __byte_perm(lo, hi, sel);
+    const unsigned short* pv = vals + (__popc(hi & mh) + __popc(lo & ml));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (byte & (0x80u >> i)) {
+            const unsigned short v = *pv;
+            ++pv;
+#pragma unroll
+            for (int g = 0; g < G; ++g) acc[i][g] = fma_h(acc[i][g], v, coef[g]);
+        }
+    }
+}
+
+template <int G>
+__device__ __forceinline__ void load_coef(const unsigned short* p, unsigned short (&c)[G]) {
+    if constexpr (G == 1) {
+        c[0] = p[0];
+    } else if constexpr (G == 2) {
+        const unsigned t = *reinterpret_cast<const unsigned*>(p);
+        c[0] = t & 0xffffu; c[1] = t >> 16;
+    } else {
+#pragma unroll
+        for (int g = 0; g < G; g += 4) {
+            const uint2 t = *reinterpret_cast<const uint2*>(p + g);
+            c[g] = t.x & 0xffffu; c[g + 1] = t.x >> 16; c[g + 2] = t.y & 0xffffu; c[g + 3] = t.y >> 16;
+        }
+    }
+}
+
+__device__ __forceinline__ void store_coef(float* p, float v) { *p = v; }
+__device__ __forceinline__ void store_coef(unsigned short* p, float v) { *p = __half_as_ushort(__float2half_rn(v)); }
+__device__ __forceinline__ float coef_value(float v) { return v; }
+// the probability that enters P.V is the fp16-rounded one; the running sum must use the same value
+__device__ __forceinline__ float round_like(const unsigned short*, float v) { return __half2float(__float2half_rn(v)); }
+__device__ __forceinline__ float round_like(const float*, float v) { return v; }
+
+__device__ __forceinline__ float coef_to_float(float v) { return v; }
+__device__ __forceinline__ float coef_to_float(unsigned short v) { return __half2float(__ushort_as_half(v)); }
+
 // Split-KV partial of one (kv head, split, q head of the group): 128 un-normalised
 // output channels, then the running max (log2 domain) and the running sum.
 constexpr int kPartialStride = kD + 4;  // floats; keeps records 16-byte aligned

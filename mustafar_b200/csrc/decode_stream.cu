@@ -39,51 +39,6 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-__device__ __forceinline__ float fma_h(float acc, unsigned short a, unsigned short b) {
-    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc) : "h"(a), "h"(b));
-    return acc;
-}
-
-// fp16-coefficient tile step (see tile_step in decode_common.cuh for the scheme)
-template <int G>
-__device__ __forceinline__ void tile_step(unsigned hi, unsigned lo, const unsigned short* vals, unsigned sel,
-                                          unsigned mh, unsigned ml, const unsigned short (&coef)[G], float (&acc)[8][G]) {
-    const unsigned byte = __byte_perm(lo, hi, sel);
-    const unsigned short* pv = vals + (__popc(hi & mh) + __popc(lo & ml));
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        if (byte & (0x80u >> i)) {
-            const unsigned short v = *pv;
-            ++pv;
-#pragma unroll
-            for (int g = 0; g < G; ++g) acc[i][g] = fma_h(acc[i][g], v, coef[g]);
-        }
-    }
-}
-
-template <int G>
-__device__ __forceinline__ void load_coef(const unsigned short* p, unsigned short (&c)[G]) {
-    if constexpr (G == 1) {
-        c[0] = p[0];
-    } else if constexpr (G == 2) {
-        const unsigned t = *reinterpret_cast<const unsigned*>(p);
-        c[0] = t & 0xffffu; c[1] = t >> 16;
-    } else {
-#pragma unroll
-        for (int g = 0; g < G; g += 4) {
-            const uint2 t = *reinterpret_cast<const uint2*>(p + g);
-            c[g] = t.x & 0xffffu; c[g + 1] = t.x >> 16; c[g + 2] = t.y & 0xffffu; c[g + 3] = t.y >> 16;
-        }
-    }
-}
-
-__device__ __forceinline__ void store_coef(float* p, float v) { *p = v; }
-__device__ __forceinline__ void store_coef(unsigned short* p, float v) { *p = __half_as_ushort(__float2half_rn(v)); }
-__device__ __forceinline__ float coef_value(float v) { return v; }
-// the probability that enters P.V is the fp16-rounded one; the running sum must use the same value
-__device__ __forceinline__ float round_like(const unsigned short*, float v) { return __half2float(__float2half_rn(v)); }
-__device__ __forceinline__ float round_like(const float*, float v) { return v; }
-
 template <int G, bool MIXED>
 struct StLayout {
     using coef_t = typename std::conditional<MIXED, unsigned short, float>::type;

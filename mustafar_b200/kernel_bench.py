@@ -35,6 +35,26 @@ def timed(fn, iters=10, warmup=3):
     return e0.elapsed_time(e1) * 1e3 / iters       # microseconds
 
 
+def timed_graph(fn, iters=10, warmup=3):
+    """Same as timed(), but the calls are captured in a CUDA graph first, which removes the host's
+    launch cost (Python + ctypes, ~20 us per call) from the figure: what a graph-replayed decode step pays."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(iters):
+            fn()
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / iters
+
+
 def emit(name, us, nbytes, **kw):
     print(json.dumps({"kernel": name, "us": round(us, 2), "algorithmic_bytes": int(nbytes),
                       "GBps": round(nbytes / us / 1e3, 1), **kw}), flush=True)
@@ -113,6 +133,8 @@ def bench_decode(quick):
         for variant in ("block", "stream16"):
             us = timed(lambda: ops.decode_attention(q, ks, vs, kw, vw, G, out=out, stage_halves=hint, variant=variant))
             emit(f"fused decode attention ({variant})", us, nbytes, batch=B, kv_len=L, window=128, sparsity=0.7)
+        us = timed_graph(lambda: ops.decode_attention(q, ks, vs, kw, vw, G, out=out, stage_halves=hint, variant="block"))
+        emit("fused decode attention (block, CUDA-graph replay)", us, nbytes, batch=B, kv_len=L, window=128, sparsity=0.7)
         ops.check_device_status()
         del ks, vs
 

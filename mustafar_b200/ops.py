@@ -144,8 +144,8 @@ def decode_attention(q: torch.Tensor, k_store: SparseStore, v_store: SparseStore
 
     q [n_kv_heads*group, 128] fp16; k_store / v_store hold the compressed tokens;
     k_window / v_window [n_kv_heads, W, 128] fp16 are the dense recent tokens (or None).
-    ``variant``: "auto" (size heuristic); "block", "superblock", "stream" or "stream16" (stream
-    kernel with fp16 coefficients) pins the kernel.
+    ``variant``: "auto" (size heuristic); "block" (fp16 coefficients), "block32" (fp32 coefficients),
+    "superblock", "stream" or "stream16" (stream kernel with fp16 coefficients) pins the kernel.
     ``window_len``: optional CUDA int32 tensor [1] with the number of valid window tokens (the window
     tensors then give the capacity); a captured launch can so be replayed while the window grows.
     Returns fp16 [n_kv_heads*group, 128].
@@ -184,7 +184,7 @@ def decode_attention(q: torch.Tensor, k_store: SparseStore, v_store: SparseStore
         v_store.bitmaps.data_ptr(), v_store.tiles_cap, v_store.accum.data_ptr(), v_store.tiles_cap + 1,
         v_store.nz.data_ptr(), None, v_store.nz_capacity,
         L, kw, vw, wh, wt, W, None if window_len is None else window_len.data_ptr(), float(softmax_scale), out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(),
-        nsplit, stage_halves, {"auto": 0, "block": 1, "superblock": 2, "stream": 4, "stream16": 12}[variant], st.data_ptr(), _stream())
+        nsplit, stage_halves, {"auto": 0, "block": 1, "block32": 17, "superblock": 2, "stream": 4, "stream16": 12}[variant], st.data_ptr(), _stream())
     _lib.check(r, "mfar_decode_attention_fp16")
     if _debug_check():
         check_device_status(q.device)

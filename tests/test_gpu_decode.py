@@ -91,7 +91,7 @@ def test_value_formulation(m, G, Bh, L):
     (4, 2, 0, 200, 0.7),          # nothing compressed yet
     (1, 2, 64, 0, 0.0),           # unpruned: every tile full, worst-case stage
 ])
-@pytest.mark.parametrize("variant", ["block", "superblock", "stream", "stream16"])
+@pytest.mark.parametrize("variant", ["block", "block32", "superblock", "stream", "stream16"])
 def test_fused_decode_attention(m, G, Bh, L, W, s, variant):
     if s > 0:
         kp, vp, ks, vs = build_cache(m, Bh, L, s, 31 + L + W)
@@ -113,7 +113,7 @@ def test_fused_decode_attention(m, G, Bh, L, W, s, variant):
         assert oracle.rel_l2(out.float().cpu(), model.float()) < 2 * TOL
 
 
-@pytest.mark.parametrize("variant", ["block", "superblock", "stream", "stream16"])
+@pytest.mark.parametrize("variant", ["block", "block32", "superblock", "stream", "stream16"])
 def test_decode_split_invariance(m, variant):
     kp, vp, ks, vs = build_cache(m, 2, 2048 + 64, 0.7, 5)     # 33 blocks: ragged last superblock
     kw, vw = oracle.make_kv(2, 128, seed=6)
