@@ -103,8 +103,30 @@ def bench_compress(quick):
         st.tokens = L
         st.append(x[:, L:], comp.keep_rank(0.7))
     emit("append 256-token block (K, prune fused)", timed(app), Bh * 256 * D * 2 * 1.47, heads=Bh, cache_tokens=L)
-    us = timed(lambda: comp.prune(x[:, :L], 0.7))
+    xc = x[:, :L].contiguous()
+    y = torch.empty_like(xc)
+    us = timed(lambda: comp.prune(xc, 0.7, out=y))
     emit("prune only", us, 2 * Bh * L * D * 2, heads=Bh, tokens=L)
+
+
+def bench_compress_fp16(quick):
+    """Only the fused prune+compress kernel (K and V, 70 %) and the prune-only kernel: few launches,
+    the case to put under a profiler."""
+    Bh, L = (16, 4096) if quick else (64, 8192)
+    for kind, name in ((comp.KEY, "K"), (comp.VALUE, "V")):
+        x = synth(Bh, L, 11, kind == comp.KEY)
+        st = comp.SparseStore(Bh, L, kind, "cuda")
+
+        def run():
+            st.tokens = 0
+            st.append(x, comp.keep_rank(0.7))
+        us = timed(run, iters=3, warmup=1)
+        emit(f"prune+compress {name} fp16", us, x.numel() * 2 + store_bytes(st), heads=Bh, tokens=L, sparsity=0.7)
+        if kind == comp.KEY:
+            y = torch.empty_like(x)
+            us = timed(lambda: comp.prune(x, 0.7, out=y), iters=3, warmup=1)
+            emit("prune only", us, 2 * x.numel() * 2, heads=Bh, tokens=L)
+        del st, x
 
 
 def make_cache(B, L, s, seed=5):
@@ -189,7 +211,7 @@ def main():
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
-    table = {"compress": bench_compress, "decode": bench_decode, "ops": bench_ops, "quant": bench_quant}
+    table = {"compress": bench_compress, "compress_fp16": bench_compress_fp16, "decode": bench_decode, "ops": bench_ops, "quant": bench_quant}
     for w in a.what.split(","):
         table[w](a.quick)
 
