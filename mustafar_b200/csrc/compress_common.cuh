@@ -11,26 +11,61 @@ constexpr unsigned long long kFlagAggregate = 1ull << 62;
 constexpr unsigned long long kFlagPrefix = 2ull << 62;
 constexpr unsigned long long kValueMask = (1ull << 62) - 1;
 
-// rank-th smallest magnitude among the 128 values held by a thread pair
-// (m[] = |x| as packed half2, 32 per thread).  Returns the fp16 bit pattern.
-__device__ __forceinline__ unsigned select_threshold(const __half2 (&m)[32], int rank) {
-    unsigned T = 0;
-#pragma unroll 1
-    for (int bit = 14; bit >= 0; --bit) {
-        const unsigned short tr = static_cast<unsigned short>(T | ((1u << bit) - 1u));
-        const __half2 t2 = __half2half2(__ushort_as_half(tr));
-        __half2 c0 = __float2half2_rn(0.f), c1 = c0, c2 = c0, c3 = c0;
+// Transposes, in place, the two 16x16 bit matrices that the low and the high halves of a[0..15] form:
+// afterwards bit j (bit 16+j) of a[b] is bit b of the low (high) half of the old a[j].  Recursive block
+// swap: bytes by prmt, then nibbles, bit pairs and bits by shift + bit-select (112 instructions).
+__device__ __forceinline__ void transpose16x16x2(unsigned (&a)[16]) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-            c0 = __hadd2(c0, __hle2(m[j + 0], t2));
-            c1 = __hadd2(c1, __hle2(m[j + 1], t2));
-            c2 = __hadd2(c2, __hle2(m[j + 2], t2));
-            c3 = __hadd2(c3, __hle2(m[j + 3], t2));
+    for (int i = 0; i < 8; ++i) {
+        const unsigned x = a[i], y = a[i + 8];
+        a[i] = __byte_perm(x, y, 0x6240);
+        a[i + 8] = __byte_perm(x, y, 0x7351);
+    }
+#pragma unroll
+    for (int s = 4; s >= 1; s >>= 1) {
+        const unsigned M = s == 4 ? 0x0f0f0f0fu : (s == 2 ? 0x33333333u : 0x55555555u);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (i & s) continue;
+            const unsigned x = a[i], y = a[i + s];
+            a[i] = (x & M) | ((y << s) & ~M);
+            a[i + s] = ((x >> s) & M) | (y & ~M);
         }
-        c0 = __hadd2(__hadd2(c0, c1), __hadd2(c2, c3));
-        int cnt = static_cast<int>(__low2float(c0) + __high2float(c0));
+    }
+}
+
+// rank-th smallest magnitude (1-based) among the 128 values held by a thread pair; w[] = the pair
+// member's 64 halves (sign bits ignored).  Returns the fp16 bit pattern, the same in both threads.
+//
+// Bit-sliced radix select: the 64 magnitudes are transposed into 15 bit planes of 2 x 32 elements
+// (element order inside a plane does not matter for counting), then the threshold is built from
+// the top bit down: `cand` marks the elements whose higher bits equal the threshold so far; if at
+// least `rank` of them have a 0 in this bit the threshold has a 0 there too, else the zeros are
+// smaller than the answer and leave, taking their count off the rank.  Per step: 2 and-not,
+// 2 popc and one shuffle to join the pair, instead of 64 compare/add on packed halves.
+__device__ __forceinline__ unsigned select_threshold(const unsigned (&w)[32], int rank) {
+    unsigned p0[16], p1[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        p0[j] = w[j] & 0x7fff7fffu;
+        p1[j] = w[16 + j] & 0x7fff7fffu;
+    }
+    transpose16x16x2(p0);
+    transpose16x16x2(p1);
+    unsigned c0 = kFull, c1 = kFull, T = 0;
+    int r = rank;
+#pragma unroll
+    for (int b = 14; b >= 0; --b) {
+        const unsigned z0 = c0 & ~p0[b], z1 = c1 & ~p1[b];
+        int cnt = __popc(z0) + __popc(z1);
         cnt += __shfl_xor_sync(kFull, cnt, 1);
-        if (cnt < rank) T |= (1u << bit);
+        const bool zero_side = r <= cnt;
+        c0 = zero_side ? z0 : (c0 ^ z0);
+        c1 = zero_side ? z1 : (c1 ^ z1);
+        if (!zero_side) {
+            r -= cnt;
+            T |= 1u << b;
+        }
     }
     return T;
 }
@@ -42,24 +77,14 @@ __device__ __forceinline__ void load_prune_row(const __half* row, int hh, int ra
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = ldg_nc_u4(src + 2 * j + hh);
     if (rank <= 0) return;
-    __half2 m[32];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const unsigned w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const unsigned a = w[e] & 0x7fff7fffu;
-            m[4 * j + e] = *reinterpret_cast<const __half2*>(&a);
-        }
-    }
-    const unsigned T = select_threshold(m, rank);
+    unsigned (&w)[32] = reinterpret_cast<unsigned (&)[32]>(v);
+    const unsigned T = select_threshold(w, rank);
     const __half2 t2 = __half2half2(__ushort_as_half(static_cast<unsigned short>(T)));
     const unsigned sign = keep_sign ? 0x80008000u : 0u;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        unsigned* w = reinterpret_cast<unsigned*>(&v[j]);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) w[e] &= (__hge2_mask(m[4 * j + e], t2) | sign);
+    for (int j = 0; j < 32; ++j) {
+        const unsigned a = w[j] & 0x7fff7fffu;
+        w[j] &= (__hge2_mask(*reinterpret_cast<const __half2*>(&a), t2) | sign);
     }
 }
 
