@@ -2,15 +2,17 @@
 //
 // One CTA (128 threads) owns one 64-token block of one head: 64 rows x 128 channels.
 //   1. each thread pair loads one 256-byte row straight into registers,
-//   2. finds the rank-th smallest magnitude of the row by a 15-step bisection on the
-//      fp16 bit pattern (packed half2 compares, counts kept in half2, one shuffle
-//      per step to join the pair) and zeroes everything below it,
-//   3. the pruned block goes to shared memory, where one thread per tile builds the
-//      64-bit bitmap (K: one channel down 64 tokens, V: 64 channels of one token),
-//   4. padded counts are scanned inside the CTA; the block's start inside its head
-//      comes from a decoupled look-back over the preceding blocks of the same head,
-//   5. nonzeros are packed in shared memory in final order and leave with 128-bit
-//      coalesced stores.
+//   2. finds the rank-th smallest magnitude of the row by a bit-sliced radix select (two
+//      16x16 bit transposes per thread, then 15 steps of and-not / popc / one shuffle) and
+//      comes out with one "kept and nonzero" flag per element; no pruned copy is made,
+//   3. the flags become the bitmaps: a V tile (64 channels of one token) is the pair's own
+//      flags, byte-interleaved; a K tile (one channel down 64 tokens) comes from a warp-wide
+//      32x32 bit transpose of the block's flag matrix,
+//   4. padded counts are scanned inside the CTA; the block's start inside its head comes
+//      from a decoupled look-back over the preceding blocks of the same head,
+//   5. kept values are packed in shared memory in final order (V: from the registers that
+//      loaded them; K: down the columns of the raw block in shared memory) and leave with
+//      128-bit coalesced stores.
 // CTAs take (head, block) from an atomic ticket, head-major, so every predecessor a
 // look-back waits for has already started; the wait is bounded all the same.
 #include "compress_common.cuh"
@@ -37,8 +39,11 @@ struct CompressParams {
 
 template <int KIND>
 __global__ void __launch_bounds__(128) compress_kernel(CompressParams p) {
-    __shared__ __align__(16) unsigned short xs[64 * kXsStride];
-    __shared__ __align__(16) unsigned short ps[64 * 128];
+    __shared__ __align__(16) unsigned short ps[64 * 128];                                       // packed values, final order
+    __shared__ __align__(16) unsigned short xs[KIND == MFAR_KIND_KEY ? 64 * kXsStride : 8];     // K: the raw block
+    __shared__ unsigned s_mask[4][64];         // K: keep flags [32-channel word][row], first channel in the top bit
+    __shared__ unsigned long long s_bmp[128];  // V: bitmaps by tile index
+    __shared__ unsigned s_cnt[128];            // V: padded counts by tile index, then the tiles' exclusive offsets
     __shared__ unsigned s_warp[4];
     __shared__ unsigned s_ticket;
     __shared__ long long s_excl;
@@ -51,37 +56,55 @@ __global__ void __launch_bounds__(128) compress_kernel(CompressParams p) {
     const int b = static_cast<int>(s_ticket) % p.nblk;
     if (h >= p.n_heads) return;
 
-    // ---- 1+2: load a row per thread pair, prune in registers, park in shared memory
+    // ---- 1+2: a thread pair loads one row (member hh takes chunks hh, 2+hh, ...), selects the
+    // threshold and ends up with one flag per element: kept and nonzero
+    const int r = tid >> 1, hh = tid & 1;
+    uint4 v[8];
     {
-        const int r = tid >> 1, hh = tid & 1;
-        uint4 v[8];
-        load_prune_row(p.x + h * p.xhs + (static_cast<int64_t>(b) * 64 + r) * p.xts, hh, p.rank, false, v);
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + h * p.xhs + (static_cast<int64_t>(b) * 64 + r) * p.xts);
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(&xs[r * kXsStride + 8 * (2 * j + hh)]) = v[j];
+        for (int j = 0; j < 8; ++j) v[j] = ldg_nc_u4(src + 2 * j + hh);
     }
-    __syncthreads();
-
-    // ---- 3: one thread per tile builds its bitmap
-    unsigned hi = 0, lo = 0;
+    const unsigned (&w)[32] = reinterpret_cast<const unsigned (&)[32]>(v);
     if (KIND == MFAR_KIND_KEY) {
-        const int c = tid;
-#pragma unroll 8
-        for (int i = 0; i < 32; ++i) hi = (hi << 1) | ((xs[i * kXsStride + c] & 0x7fffu) != 0);
-#pragma unroll 8
-        for (int i = 32; i < 64; ++i) lo = (lo << 1) | ((xs[i * kXsStride + c] & 0x7fffu) != 0);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(&xs[r * kXsStride + 8 * (2 * j + hh)]) = v[j];
+    }
+    const RowSelect sel = select_row(w, p.rank);
+    // flags in bitmap order, one byte per chunk; with the partner's they give the row's two 64-bit masks
+    const unsigned y0 = plane_to_bitmap_order(sel.keep0), y1 = plane_to_bitmap_order(sel.keep1);
+    const unsigned q0 = __shfl_xor_sync(kFull, y0, 1), q1 = __shfl_xor_sync(kFull, y1, 1);
+    unsigned hi0, lo0, hi1, lo1;
+    interleave_chunk_bytes(hh ? q0 : y0, hh ? y0 : q0, hi0, lo0);   // channels 0..63
+    interleave_chunk_bytes(hh ? q1 : y1, hh ? y1 : q1, hi1, lo1);   // channels 64..127
+
+    // ---- 3: bitmap of the tile this thread answers for
+    unsigned hi, lo;
+    if (KIND == MFAR_KIND_KEY) {
+        // tile = channel tid down the 64 rows: transpose the block's flag matrix, 32 x 32 bits per warp step
+        if (hh == 0) {
+            s_mask[0][r] = hi0;
+            s_mask[1][r] = lo0;
+        } else {
+            s_mask[2][r] = hi1;
+            s_mask[3][r] = lo1;
+        }
+        __syncthreads();
+        hi = __brev(warp_transpose32(__brev(s_mask[warp][lane])));
+        lo = __brev(warp_transpose32(__brev(s_mask[warp][32 + lane])));
     } else {
-        const int hf = tid >> 6, i = tid & 63;
-        const unsigned short* row = &xs[i * kXsStride + hf * 64];
-#pragma unroll 8
-        for (int e = 0; e < 32; ++e) hi = (hi << 1) | ((row[e] & 0x7fffu) != 0);
-#pragma unroll 8
-        for (int e = 32; e < 64; ++e) lo = (lo << 1) | ((row[e] & 0x7fffu) != 0);
+        // tile = (channel half hh, row r), index hh * 64 + r; the scan below runs in index order
+        hi = hh ? hi1 : hi0;
+        lo = hh ? lo1 : lo0;
+        const unsigned n = __popc(hi) + __popc(lo);
+        s_bmp[hh * 64 + r] = (static_cast<unsigned long long>(hi) << 32) | lo;
+        s_cnt[hh * 64 + r] = ((n + 7u) & ~7u) >> 1;
+        __syncthreads();
     }
     const unsigned nnz = __popc(hi) + __popc(lo);
-    const unsigned pad = ((nnz + 7u) & ~7u) >> 1;  // uint32 units, reference counts
+    const unsigned pad = (KIND == MFAR_KIND_KEY) ? (((nnz + 7u) & ~7u) >> 1) : s_cnt[tid];  // uint32 units, reference counts
 
-    // ---- 4a: CTA scan of the 128 padded counts
+    // ---- 4a: CTA scan of the 128 padded counts (thread tid = tile tid)
     unsigned incl = pad;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
@@ -92,13 +115,14 @@ __global__ void __launch_bounds__(128) compress_kernel(CompressParams p) {
     __syncthreads();
     unsigned wbase = 0, total = 0;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-        const unsigned t = s_warp[w];
-        if (w < warp) wbase += t;
+    for (int wi = 0; wi < 4; ++wi) {
+        const unsigned t = s_warp[wi];
+        if (wi < warp) wbase += t;
         total += t;
     }
     incl += wbase;
     const unsigned excl_tile = incl - pad;
+    if (KIND == MFAR_KIND_VALUE) s_cnt[tid] = excl_tile;   // own entry only; read by others after the next barrier
 
     // ---- 4b: start of this block inside its head (decoupled look-back, warp 0)
     if (warp == 0) {
@@ -113,7 +137,8 @@ __global__ void __launch_bounds__(128) compress_kernel(CompressParams p) {
     const long long base = (p.tile_start > 0) ? static_cast<long long>(acc[p.tile_start]) : 0ll;
     const long long blk_start = base + s_excl;  // uint32 units inside the head
 
-    p.bmp[h * p.bmp_hs + tile0 + tid] = (static_cast<unsigned long long>(hi) << 32) | lo;
+    p.bmp[h * p.bmp_hs + tile0 + tid] =
+        (KIND == MFAR_KIND_KEY) ? ((static_cast<unsigned long long>(hi) << 32) | lo) : s_bmp[tid];
     acc[tile0 + tid + 1] = static_cast<int>(blk_start + incl);
     if (p.tile_start == 0 && b == 0 && tid == 0) acc[0] = 0;
 
@@ -125,26 +150,40 @@ __global__ void __launch_bounds__(128) compress_kernel(CompressParams p) {
     }
 
     // ---- 5: pack in shared memory in final order, then stream out
-    {
+    if (KIND == MFAR_KIND_KEY) {
         unsigned o = 2 * excl_tile;
         const unsigned end = 2 * incl;
-        if (KIND == MFAR_KIND_KEY) {
-            const int c = tid;
+        const int c = tid;
 #pragma unroll 8
-            for (int i = 0; i < 64; ++i) {
-                const unsigned short u = xs[i * kXsStride + c];
-                if (u & 0x7fffu) ps[o++] = u;
+        for (int i = 0; i < 32; ++i)
+            if ((hi >> (31 - i)) & 1u) ps[o++] = xs[i * kXsStride + c];
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i)
+            if ((lo >> (31 - i)) & 1u) ps[o++] = xs[(32 + i) * kXsStride + c];
+        while (o < end) ps[o++] = 0;
+    } else {
+        // straight from the registers: this member's chunks of both tiles of row r
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const unsigned thi = t ? hi1 : hi0, tlo = t ? lo1 : lo0, y = t ? y1 : y0;
+            const unsigned long long bm = (static_cast<unsigned long long>(thi) << 32) | tlo;
+            const unsigned off = 2 * s_cnt[t * 64 + r];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int cidx = 2 * k + hh;                        // chunk inside the tile
+                unsigned o = off + (cidx ? __popcll(bm >> (64 - 8 * cidx)) : 0);
+                const unsigned flags = y >> (24 - 8 * k);           // bit 7 = first element of the chunk
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const unsigned word = w[16 * t + 4 * k + (e >> 1)];
+                    if ((flags >> (7 - e)) & 1u) ps[o++] = static_cast<unsigned short>((e & 1) ? (word >> 16) : word);
+                }
             }
-        } else {
-            const int hf = tid >> 6, i = tid & 63;
-            const unsigned short* row = &xs[i * kXsStride + hf * 64];
-#pragma unroll 8
-            for (int e = 0; e < 64; ++e) {
-                const unsigned short u = row[e];
-                if (u & 0x7fffu) ps[o++] = u;
+            if (hh == t) {   // the tile's owner zero-fills up to the padded length
+                const unsigned n = __popcll(bm);
+                for (unsigned o = off + n; o < off + ((n + 7u) & ~7u); ++o) ps[o] = 0;
             }
         }
-        while (o < end) ps[o++] = 0;
     }
     __syncthreads();
     {

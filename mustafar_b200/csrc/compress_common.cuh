@@ -3,6 +3,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "compress_bits.cuh"
 
 namespace mfar {
 
@@ -11,39 +12,24 @@ constexpr unsigned long long kFlagAggregate = 1ull << 62;
 constexpr unsigned long long kFlagPrefix = 2ull << 62;
 constexpr unsigned long long kValueMask = (1ull << 62) - 1;
 
-// Transposes, in place, the two 16x16 bit matrices that the low and the high halves of a[0..15] form:
-// afterwards bit j (bit 16+j) of a[b] is bit b of the low (high) half of the old a[j].  Recursive block
-// swap: bytes by prmt, then nibbles, bit pairs and bits by shift + bit-select (112 instructions).
-__device__ __forceinline__ void transpose16x16x2(unsigned (&a)[16]) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const unsigned x = a[i], y = a[i + 8];
-        a[i] = __byte_perm(x, y, 0x6240);
-        a[i + 8] = __byte_perm(x, y, 0x7351);
-    }
-#pragma unroll
-    for (int s = 4; s >= 1; s >>= 1) {
-        const unsigned M = s == 4 ? 0x0f0f0f0fu : (s == 2 ? 0x33333333u : 0x55555555u);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            if (i & s) continue;
-            const unsigned x = a[i], y = a[i + s];
-            a[i] = (x & M) | ((y << s) & ~M);
-            a[i + s] = ((x >> s) & M) | (y & ~M);
-        }
-    }
-}
+// Result of the per-row selection for one member of the thread pair that owns the row.
+struct RowSelect {
+    unsigned T;             // fp16 bit pattern of the rank-th smallest magnitude (same in both members)
+    unsigned keep0, keep1;  // plane-layout flags (see plane_to_bitmap_order) of the member's chunks 0..3 and
+                            // 4..7: the element survives pruning AND is not zero
+};
 
 // rank-th smallest magnitude (1-based) among the 128 values held by a thread pair; w[] = the pair
-// member's 64 halves (sign bits ignored).  Returns the fp16 bit pattern, the same in both threads.
+// member's 64 halves (sign bits ignored).  rank <= 0: no pruning (T = 0, every nonzero kept).
 //
 // Bit-sliced radix select: the 64 magnitudes are transposed into 15 bit planes of 2 x 32 elements
 // (element order inside a plane does not matter for counting), then the threshold is built from
 // the top bit down: `cand` marks the elements whose higher bits equal the threshold so far; if at
-// least `rank` of them have a 0 in this bit the threshold has a 0 there too, else the zeros are
-// smaller than the answer and leave, taking their count off the rank.  Per step: 2 and-not,
-// 2 popc and one shuffle to join the pair, instead of 64 compare/add on packed halves.
-__device__ __forceinline__ unsigned select_threshold(const unsigned (&w)[32], int rank) {
+// least `rank` of them have a 0 in this bit the threshold has a 0 there too and the ones are known
+// to be greater, else the zeros are smaller than the answer and leave, taking their count off the
+// rank.  Per step: 2 and-not, 2 popc and one shuffle to join the pair, instead of 64 compare/add
+// on packed halves.  What is greater than or still equal to the threshold at the end is kept.
+__device__ __forceinline__ RowSelect select_row(const unsigned (&w)[32], int rank) {
     unsigned p0[16], p1[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
@@ -52,22 +38,55 @@ __device__ __forceinline__ unsigned select_threshold(const unsigned (&w)[32], in
     }
     transpose16x16x2(p0);
     transpose16x16x2(p1);
-    unsigned c0 = kFull, c1 = kFull, T = 0;
-    int r = rank;
+    unsigned c0 = kFull, c1 = kFull, g0 = 0, g1 = 0, T = 0;
+    if (rank > 0) {
+        int r = rank;
 #pragma unroll
-    for (int b = 14; b >= 0; --b) {
-        const unsigned z0 = c0 & ~p0[b], z1 = c1 & ~p1[b];
-        int cnt = __popc(z0) + __popc(z1);
-        cnt += __shfl_xor_sync(kFull, cnt, 1);
-        const bool zero_side = r <= cnt;
-        c0 = zero_side ? z0 : (c0 ^ z0);
-        c1 = zero_side ? z1 : (c1 ^ z1);
-        if (!zero_side) {
-            r -= cnt;
-            T |= 1u << b;
+        for (int b = 14; b >= 0; --b) {
+            const unsigned z0 = c0 & ~p0[b], z1 = c1 & ~p1[b];
+            int cnt = __popc(z0) + __popc(z1);
+            cnt += __shfl_xor_sync(kFull, cnt, 1);
+            const bool zero_side = r <= cnt;
+            const unsigned o0 = c0 ^ z0, o1 = c1 ^ z1;   // candidates with a 1 in this bit
+            g0 |= zero_side ? o0 : 0u;
+            g1 |= zero_side ? o1 : 0u;
+            c0 = zero_side ? z0 : o0;
+            c1 = zero_side ? z1 : o1;
+            if (!zero_side) {
+                r -= cnt;
+                T |= 1u << b;
+            }
         }
     }
-    return T;
+    RowSelect res;
+    res.T = T;
+    res.keep0 = g0 | c0;
+    res.keep1 = g1 | c1;
+    if (T == 0) {   // zeros pass a zero threshold but never enter a bitmap
+        unsigned n0 = 0, n1 = 0;
+#pragma unroll
+        for (int b = 0; b < 15; ++b) {
+            n0 |= p0[b];
+            n1 |= p1[b];
+        }
+        res.keep0 &= n0;
+        res.keep1 &= n1;
+    }
+    return res;
+}
+
+__device__ __forceinline__ unsigned select_threshold(const unsigned (&w)[32], int rank) { return select_row(w, rank).T; }
+
+// 32 x 32 bit transpose across a warp: lane i passes row i, lane j returns column j (bit i = bit j of lane i's x).
+__device__ __forceinline__ unsigned warp_transpose32(unsigned x) {
+    const unsigned lane = lane_id();
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        const unsigned m = s == 16 ? 0x0000ffffu : s == 8 ? 0x00ff00ffu : s == 4 ? 0x0f0f0f0fu : s == 2 ? 0x33333333u : 0x55555555u;
+        const unsigned y = __shfl_xor_sync(kFull, x, s);
+        x = (lane & s) ? (((y >> s) & m) | (x & ~m)) : ((x & m) | ((y << s) & ~m));
+    }
+    return x;
 }
 
 // Loads the pair's half of a row (chunks 2j+hh of 8 halves) and prunes it in registers.
