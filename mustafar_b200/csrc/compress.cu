@@ -19,6 +19,10 @@
 
 namespace mfar {
 
+#ifndef MFAR_COMPRESS_MIN_CTAS
+#define MFAR_COMPRESS_MIN_CTAS 5
+#endif
+
 struct CompressParams {
     const __half* x;
     int64_t xhs, xts;
@@ -38,160 +42,181 @@ struct CompressParams {
 };
 
 template <int KIND>
-__global__ void __launch_bounds__(128) compress_kernel(CompressParams p) {
+__global__ void __launch_bounds__(128, MFAR_COMPRESS_MIN_CTAS) compress_kernel(CompressParams p) {
     __shared__ __align__(16) unsigned short ps[64 * 128];                                       // packed values, final order
     __shared__ __align__(16) unsigned short xs[KIND == MFAR_KIND_KEY ? 64 * kXsStride : 8];     // K: the raw block
     __shared__ unsigned s_mask[4][64];         // K: keep flags [32-channel word][row], first channel in the top bit
-    __shared__ unsigned long long s_bmp[128];  // V: bitmaps by tile index
-    __shared__ unsigned s_cnt[128];            // V: padded counts by tile index, then the tiles' exclusive offsets
-    __shared__ unsigned s_warp[4];
+    __shared__ unsigned s_warp[4][2];
     __shared__ unsigned s_ticket;
     __shared__ long long s_excl;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) s_ticket = atomicAdd(p.ticket, 1u);
-    __syncthreads();
-    const int h = static_cast<int>(s_ticket) / p.nblk;
-    const int b = static_cast<int>(s_ticket) % p.nblk;
-    if (h >= p.n_heads) return;
+    const int r = tid >> 1, hh = tid & 1;      // row of the block and member of the pair that owns it
+    const unsigned n_blocks = static_cast<unsigned>(p.n_heads) * static_cast<unsigned>(p.nblk);
 
-    // ---- 1+2: a thread pair loads one row (member hh takes chunks hh, 2+hh, ...), selects the
-    // threshold and ends up with one flag per element: kept and nonzero
-    const int r = tid >> 1, hh = tid & 1;
-    uint4 v[8];
+    // (head, block) pairs come from an atomic ticket, fetched when the CTA is ready to start on it: blocks
+    // then start in ticket order, and a look-back never waits for a predecessor that has not begun.
     {
-        const uint4* src = reinterpret_cast<const uint4*>(p.x + h * p.xhs + (static_cast<int64_t>(b) * 64 + r) * p.xts);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = ldg_nc_u4(src + 2 * j + hh);
-    }
-    const unsigned (&w)[32] = reinterpret_cast<const unsigned (&)[32]>(v);
-    if (KIND == MFAR_KIND_KEY) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(&xs[r * kXsStride + 8 * (2 * j + hh)]) = v[j];
-    }
-    const RowSelect sel = select_row(w, p.rank);
-    // flags in bitmap order, one byte per chunk; with the partner's they give the row's two 64-bit masks
-    const unsigned y0 = plane_to_bitmap_order(sel.keep0), y1 = plane_to_bitmap_order(sel.keep1);
-    const unsigned q0 = __shfl_xor_sync(kFull, y0, 1), q1 = __shfl_xor_sync(kFull, y1, 1);
-    unsigned hi0, lo0, hi1, lo1;
-    interleave_chunk_bytes(hh ? q0 : y0, hh ? y0 : q0, hi0, lo0);   // channels 0..63
-    interleave_chunk_bytes(hh ? q1 : y1, hh ? y1 : q1, hi1, lo1);   // channels 64..127
+        if (tid == 0) s_ticket = atomicAdd(p.ticket, 1u);
+        __syncthreads();
+        const unsigned ticket = s_ticket;
+        if (ticket >= n_blocks) return;
+        const int h = static_cast<int>(ticket / static_cast<unsigned>(p.nblk));
+        const int b = static_cast<int>(ticket % static_cast<unsigned>(p.nblk));
 
-    // ---- 3: bitmap of the tile this thread answers for
-    unsigned hi, lo;
-    if (KIND == MFAR_KIND_KEY) {
-        // tile = channel tid down the 64 rows: transpose the block's flag matrix, 32 x 32 bits per warp step
-        if (hh == 0) {
-            s_mask[0][r] = hi0;
-            s_mask[1][r] = lo0;
-        } else {
-            s_mask[2][r] = hi1;
-            s_mask[3][r] = lo1;
+        // ---- 1+2: the pair loads one row (member hh takes chunks hh, 2+hh, ...), selects the
+        // threshold and ends up with one flag per element: kept and nonzero
+        uint4 v[8];
+        {
+            const uint4* src = reinterpret_cast<const uint4*>(p.x + h * p.xhs + (static_cast<int64_t>(b) * 64 + r) * p.xts);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = ldg_nc_u4(src + 2 * j + hh);
         }
-        __syncthreads();
-        hi = __brev(warp_transpose32(__brev(s_mask[warp][lane])));
-        lo = __brev(warp_transpose32(__brev(s_mask[warp][32 + lane])));
-    } else {
-        // tile = (channel half hh, row r), index hh * 64 + r; the scan below runs in index order
-        hi = hh ? hi1 : hi0;
-        lo = hh ? lo1 : lo0;
-        const unsigned n = __popc(hi) + __popc(lo);
-        s_bmp[hh * 64 + r] = (static_cast<unsigned long long>(hi) << 32) | lo;
-        s_cnt[hh * 64 + r] = ((n + 7u) & ~7u) >> 1;
-        __syncthreads();
-    }
-    const unsigned nnz = __popc(hi) + __popc(lo);
-    const unsigned pad = (KIND == MFAR_KIND_KEY) ? (((nnz + 7u) & ~7u) >> 1) : s_cnt[tid];  // uint32 units, reference counts
-
-    // ---- 4a: CTA scan of the 128 padded counts (thread tid = tile tid)
-    unsigned incl = pad;
+        const unsigned (&w)[32] = reinterpret_cast<const unsigned (&)[32]>(v);
+        if (KIND == MFAR_KIND_KEY) {
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        const unsigned n = __shfl_up_sync(kFull, incl, d);
-        if (lane >= d) incl += n;
-    }
-    if (lane == 31) s_warp[warp] = incl;
-    __syncthreads();
-    unsigned wbase = 0, total = 0;
+            for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(&xs[r * kXsStride + 8 * (2 * j + hh)]) = v[j];
+        }
+        const RowSelect sel = select_row(w, p.rank);
+        // flags in bitmap order, one byte per chunk; with the partner's they give the row's two 64-bit masks
+        const unsigned y0 = plane_to_bitmap_order(sel.keep0), y1 = plane_to_bitmap_order(sel.keep1);
+        const unsigned q0 = __shfl_xor_sync(kFull, y0, 1), q1 = __shfl_xor_sync(kFull, y1, 1);
+        unsigned hi0, lo0, hi1, lo1;
+        interleave_chunk_bytes(hh ? q0 : y0, hh ? y0 : q0, hi0, lo0);   // channels 0..63
+        interleave_chunk_bytes(hh ? q1 : y1, hh ? y1 : q1, hi1, lo1);   // channels 64..127
+
+        // ---- 3+4a: bitmap and padded count of the tile this thread answers for, offsets inside the block
+        unsigned hi, lo, pad, incl, total;
+        int tile;                                  // index of that tile inside the block
+        if (KIND == MFAR_KIND_KEY) {
+            // tile = channel tid down the 64 rows: transpose the block's flag matrix, 32 x 32 bits per warp step
+            if (hh == 0) {
+                s_mask[0][r] = hi0;
+                s_mask[1][r] = lo0;
+            } else {
+                s_mask[2][r] = hi1;
+                s_mask[3][r] = lo1;
+            }
+            __syncthreads();
+            hi = __brev(warp_transpose32(__brev(s_mask[warp][lane])));
+            lo = __brev(warp_transpose32(__brev(s_mask[warp][32 + lane])));
+            tile = tid;
+            const unsigned nnz = __popc(hi) + __popc(lo);
+            pad = ((nnz + 7u) & ~7u) >> 1;         // uint32 units, reference counts
+            incl = pad;
 #pragma unroll
-    for (int wi = 0; wi < 4; ++wi) {
-        const unsigned t = s_warp[wi];
-        if (wi < warp) wbase += t;
-        total += t;
-    }
-    incl += wbase;
-    const unsigned excl_tile = incl - pad;
-    if (KIND == MFAR_KIND_VALUE) s_cnt[tid] = excl_tile;   // own entry only; read by others after the next barrier
+            for (int d = 1; d < 32; d <<= 1) {
+                const unsigned n = __shfl_up_sync(kFull, incl, d);
+                if (lane >= d) incl += n;
+            }
+            if (lane == 31) s_warp[warp][0] = incl;
+            __syncthreads();
+            total = 0;
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                const unsigned t = s_warp[wi][0];
+                if (wi < warp) incl += t;
+                total += t;
+            }
+        } else {
+            // tile = (channel half hh, row r), index hh * 64 + r: scan over the rows for each half
+            // (lanes two apart), all of half 0 comes before half 1
+            hi = hh ? hi1 : hi0;
+            lo = hh ? lo1 : lo0;
+            tile = hh * 64 + r;
+            const unsigned nnz = __popc(hi) + __popc(lo);
+            pad = ((nnz + 7u) & ~7u) >> 1;
+            incl = pad;
+#pragma unroll
+            for (int d = 2; d < 32; d <<= 1) {
+                const unsigned n = __shfl_up_sync(kFull, incl, d);
+                if (lane >= d) incl += n;
+            }
+            if (lane >= 30) s_warp[warp][hh] = incl;
+            __syncthreads();
+            unsigned half0 = 0;
+            total = 0;
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                const unsigned t0 = s_warp[wi][0], t1 = s_warp[wi][1];
+                if (wi < warp) incl += hh ? t1 : t0;
+                half0 += t0;
+                total += t0 + t1;
+            }
+            if (hh) incl += half0;
+        }
+        const unsigned excl_tile = incl - pad;
+        unsigned long long* chain = p.state + static_cast<int64_t>(h) * p.nblk;
+        if (tid == 0) lookback_announce(chain, b, 0, total);
 
-    // ---- 4b: start of this block inside its head (decoupled look-back, warp 0)
-    if (warp == 0) {
-        const long long e = lookback_exclusive(p.state + static_cast<int64_t>(h) * p.nblk, b, 0, total, p.err, p.dev_status);
-        if (lane == 0) s_excl = e;
-    }
-    __syncthreads();
-    if (s_excl < 0) return;
-
-    const int64_t tile0 = p.tile_start + static_cast<int64_t>(b) * kTilesPerBlock;
-    int* acc = p.acc + h * p.acc_hs;
-    const long long base = (p.tile_start > 0) ? static_cast<long long>(acc[p.tile_start]) : 0ll;
-    const long long blk_start = base + s_excl;  // uint32 units inside the head
-
-    p.bmp[h * p.bmp_hs + tile0 + tid] =
-        (KIND == MFAR_KIND_KEY) ? ((static_cast<unsigned long long>(hi) << 32) | lo) : s_bmp[tid];
-    acc[tile0 + tid + 1] = static_cast<int>(blk_start + incl);
-    if (p.tile_start == 0 && b == 0 && tid == 0) acc[0] = 0;
-
-    if (tid == 0 && p.max_block) atomicMax(p.max_block, 2u * total);
-
-    if (2 * (blk_start + total) > p.nz_cap) {
-        if (tid == 0 && p.dev_status) atomicOr(p.dev_status, MFAR_DEV_CAPACITY);
-        return;
-    }
-
-    // ---- 5: pack in shared memory in final order, then stream out
-    if (KIND == MFAR_KIND_KEY) {
-        unsigned o = 2 * excl_tile;
-        const unsigned end = 2 * incl;
-        const int c = tid;
+        // ---- 5: pack in shared memory in final order (needs no global offset yet)
+        if (KIND == MFAR_KIND_KEY) {
+            unsigned o = 2 * excl_tile;
+            const unsigned end = 2 * incl;
+            const int c = tid;
 #pragma unroll 8
-        for (int i = 0; i < 32; ++i)
-            if ((hi >> (31 - i)) & 1u) ps[o++] = xs[i * kXsStride + c];
+            for (int i = 0; i < 32; ++i)
+                if ((hi >> (31 - i)) & 1u) ps[o++] = xs[i * kXsStride + c];
 #pragma unroll 8
-        for (int i = 0; i < 32; ++i)
-            if ((lo >> (31 - i)) & 1u) ps[o++] = xs[(32 + i) * kXsStride + c];
-        while (o < end) ps[o++] = 0;
-    } else {
-        // straight from the registers: this member's chunks of both tiles of row r
+            for (int i = 0; i < 32; ++i)
+                if ((lo >> (31 - i)) & 1u) ps[o++] = xs[(32 + i) * kXsStride + c];
+            while (o < end) ps[o++] = 0;
+        } else {
+            // straight from the registers: this member's chunks of both tiles of row r
+            const unsigned excl_other = __shfl_xor_sync(kFull, excl_tile, 1);
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-            const unsigned thi = t ? hi1 : hi0, tlo = t ? lo1 : lo0, y = t ? y1 : y0;
-            const unsigned long long bm = (static_cast<unsigned long long>(thi) << 32) | tlo;
-            const unsigned off = 2 * s_cnt[t * 64 + r];
+            for (int t = 0; t < 2; ++t) {
+                const unsigned thi = t ? hi1 : hi0, tlo = t ? lo1 : lo0, y = t ? y1 : y0;
+                const unsigned long long bm = (static_cast<unsigned long long>(thi) << 32) | tlo;
+                const unsigned off = 2 * (hh == t ? excl_tile : excl_other);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int cidx = 2 * k + hh;                        // chunk inside the tile
-                unsigned o = off + (cidx ? __popcll(bm >> (64 - 8 * cidx)) : 0);
-                const unsigned flags = y >> (24 - 8 * k);           // bit 7 = first element of the chunk
+                for (int k = 0; k < 4; ++k) {
+                    const int cidx = 2 * k + hh;                        // chunk inside the tile
+                    unsigned o = off + (cidx ? __popcll(bm >> (64 - 8 * cidx)) : 0);
+                    const unsigned flags = y >> (24 - 8 * k);           // bit 7 = first element of the chunk
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    const unsigned word = w[16 * t + 4 * k + (e >> 1)];
-                    if ((flags >> (7 - e)) & 1u) ps[o++] = static_cast<unsigned short>((e & 1) ? (word >> 16) : word);
+                    for (int e = 0; e < 8; ++e) {
+                        const unsigned word = w[16 * t + 4 * k + (e >> 1)];
+                        if ((flags >> (7 - e)) & 1u) ps[o++] = static_cast<unsigned short>((e & 1) ? (word >> 16) : word);
+                    }
+                }
+                if (hh == t) {   // the tile's owner zero-fills up to the padded length
+                    const unsigned n = __popcll(bm);
+                    for (unsigned o = off + n; o < off + ((n + 7u) & ~7u); ++o) ps[o] = 0;
                 }
             }
-            if (hh == t) {   // the tile's owner zero-fills up to the padded length
-                const unsigned n = __popcll(bm);
-                for (unsigned o = off + n; o < off + ((n + 7u) & ~7u); ++o) ps[o] = 0;
-            }
         }
-    }
-    __syncthreads();
-    {
-        __half* head_nz = p.nz + (p.nz_off ? 8ll * p.nz_off[h] : h * p.nz_hs);
-        uint4* dst = reinterpret_cast<uint4*>(head_nz + 2 * blk_start);
-        const uint4* src = reinterpret_cast<const uint4*>(ps);
-        const int n16 = static_cast<int>(total >> 2);
-        for (int i = tid; i < n16; i += 128) dst[i] = src[i];
+
+        // ---- 4b: start of this block inside its head (decoupled look-back, warp 0; the predecessors
+        // announced their totals a pack phase ago)
+        if (warp == 0) {
+            const long long e = lookback_exclusive(chain, b, 0, total, p.err, p.dev_status, false);
+            if (lane == 0) s_excl = e;
+        }
+        __syncthreads();
+        if (s_excl < 0) return;
+
+        const int64_t tile0 = p.tile_start + static_cast<int64_t>(b) * kTilesPerBlock;
+        int* acc = p.acc + h * p.acc_hs;
+        const long long base = (p.tile_start > 0) ? static_cast<long long>(acc[p.tile_start]) : 0ll;
+        const long long blk_start = base + s_excl;  // uint32 units inside the head
+
+        p.bmp[h * p.bmp_hs + tile0 + tile] = (static_cast<unsigned long long>(hi) << 32) | lo;
+        acc[tile0 + tile + 1] = static_cast<int>(blk_start + incl);
+        if (p.tile_start == 0 && b == 0 && tid == 0) acc[0] = 0;
+        if (tid == 0 && p.max_block) atomicMax(p.max_block, 2u * total);
+
+        if (2 * (blk_start + total) > p.nz_cap) {
+            // the values of this block are dropped; later blocks still run
+            if (tid == 0 && p.dev_status) atomicOr(p.dev_status, MFAR_DEV_CAPACITY);
+        } else {
+            __half* head_nz = p.nz + (p.nz_off ? 8ll * p.nz_off[h] : h * p.nz_hs);
+            uint4* dst = reinterpret_cast<uint4*>(head_nz + 2 * blk_start);
+            const uint4* src = reinterpret_cast<const uint4*>(ps);
+            const int n16 = static_cast<int>(total >> 2);
+            for (int i = tid; i < n16; i += 128) dst[i] = src[i];
+        }
     }
 }
 
@@ -267,7 +292,8 @@ extern "C" int mfar_compress_fp16(const void* x, int64_t x_head_stride, int64_t 
     p.dev_status = dev_status;
     p.max_block = max_block_halves;
 
-    const unsigned grid = static_cast<unsigned>(n_heads) * static_cast<unsigned>(nblk);
+    const unsigned n_blocks = static_cast<unsigned>(n_heads) * static_cast<unsigned>(nblk);
+    const unsigned grid = n_blocks;
     if (kind == MFAR_KIND_KEY)
         compress_kernel<MFAR_KIND_KEY><<<grid, 128, 0, s>>>(p);
     else

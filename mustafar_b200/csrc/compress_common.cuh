@@ -107,17 +107,50 @@ __device__ __forceinline__ void load_prune_row(const __half* row, int hh, int ra
     }
 }
 
+// Early half of the look-back, for kernels that have other work to do before they need their prefix:
+// one thread announces the block's total as soon as it is known (the chain's first block can publish
+// its inclusive prefix right away); lookback_exclusive(..., publish_aggregate = false) follows later.
+__device__ __forceinline__ void lookback_announce(unsigned long long* st, int b, int first, unsigned total) {
+    // max, not store: a warp of the same CTA may already have published the inclusive prefix, which ranks higher
+    atomicMax(st + b, (b > first ? kFlagAggregate : kFlagPrefix) | total);
+}
+
+// Waits until the shared-memory counter `c` (bumped by other warps of the same CTA) reaches `target`.
+// Called by a whole warp: lane 0 polls, everybody gets the verdict.  False after the wall-time limit.
+__device__ __forceinline__ bool wait_shared_counter(const unsigned* c, unsigned target) {
+    bool ok = true;
+    if (lane_id() == 0) {
+        const volatile unsigned* vc = c;
+        unsigned spins = 0;
+        unsigned long long t0 = 0;
+        while (static_cast<int>(*vc - target) < 0) {
+            if ((++spins & 255u) == 0) {
+                const unsigned long long now = global_timer_ns();
+                if (t0 == 0) t0 = now;
+                if (now - t0 > kWaitLimitNs) {
+                    ok = false;
+                    break;
+                }
+            }
+            __nanosleep(20);
+        }
+        __threadfence_block();
+    }
+    return __shfl_sync(kFull, ok ? 1 : 0, 0) != 0;
+}
+
 // Exclusive prefix of `total` over the chain of blocks [first, b) whose status words live in
 // `st` (indexed by chain position).  Called by one whole warp; every lane returns the same
 // value, or -1 after a bounded wait gave up (the error words are set).  The block's own
 // inclusive prefix is published in any case so that successors never wait for it.
 __device__ __forceinline__ long long lookback_exclusive(unsigned long long* st, int b, int first, unsigned total,
-                                                        unsigned* err, unsigned* dev_status) {
+                                                        unsigned* err, unsigned* dev_status,
+                                                        bool publish_aggregate = true) {
     const int lane = threadIdx.x & 31;
     long long excl = 0;
     bool failed = false;
     if (b > first) {
-        if (lane == 0) st_volatile_u64(st + b, kFlagAggregate | total);
+        if (publish_aggregate && lane == 0) st_volatile_u64(st + b, kFlagAggregate | total);
         int j = b - 1;
         while (true) {
             const int idx = j - lane;
