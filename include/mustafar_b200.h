@@ -245,6 +245,31 @@ int mfar_decode_attention_quant(
     float softmax_scale, void* out, int64_t out_stride, void* workspace, size_t workspace_bytes, int nsplit,
     uint32_t* dev_status, void* stream);
 
+/* ---- decode-step glue (no counterpart in the reference's extensions: its model file does these with torch ops) ----
+ * Three small fused kernels for the one-token decode step around the sparse attention, so that a layer is a
+ * handful of launches.  All tensors fp16, contiguous rows; rounding follows the torch expressions they replace
+ * (each elementwise op in fp32, rounded to fp16 once; RMS statistics in fp32). */
+
+/* x[r] += delta[r] (skipped when delta is NULL), then out[r] = fp16(x[r] * rsqrt(mean(x[r]^2) + eps)) * weight:
+ * the residual add and the RMSNorm that follows it (HF LlamaRMSNorm as called at models/llama_mustafar_kernel.py:744,760).
+ * hidden % 8 == 0, pointers 16-byte aligned. */
+int mfar_add_rmsnorm_f16(void* x, const void* delta, const void* weight, void* out, int64_t rows, int hidden,
+                         float eps, void* stream);
+
+/* qkv [batch, n_q_heads + 2*n_kv_heads, 128]: the fused q|k|v projection of one new token per sequence.
+ * Rotary embedding (rotate-half, inv_freq[64] fp32, cos/sin rounded to fp16) on q and k
+ * (models/llama_mustafar_kernel.py:373-374); q goes to q_out [batch*n_q_heads, 128]; k and v go into the dense
+ * windows [batch*n_kv_heads][slot] (the torch.cat of :391 and :430 without the copy).  Position and slot are read from
+ * pos_dev / slot_dev (int32 on the device) when those are not NULL, so that a captured CUDA graph can be replayed
+ * while they advance; else from pos / slot. */
+int mfar_rope_append_f16(const void* qkv, const float* inv_freq, const int32_t* pos_dev, int pos,
+                         const int32_t* slot_dev, int slot, int batch, int n_q_heads, int n_kv_heads,
+                         void* q_out, void* k_window, void* v_window, int64_t win_head_stride,
+                         int64_t win_token_stride, void* stream);
+
+/* out[r, j] = fp16(silu(gate_up[r, j])) * gate_up[r, width + j], gate_up [rows, 2*width] (HF LlamaMLP). */
+int mfar_silu_mul_f16(const void* gate_up, void* out, int64_t rows, int width, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

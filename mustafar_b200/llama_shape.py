@@ -25,7 +25,7 @@ import torch
 import torch.nn.functional as F
 
 from . import compression as comp
-from . import ops
+from . import ops, step_ops
 
 D = 128
 
@@ -123,6 +123,8 @@ class SparseLlama:
         self._stage_hint = None
         self._graph = None
         self._eager_done = False
+        self._inv_freq = None
+        self._qbuf = None
 
     # ------------------------------------------------------------------ pieces
     def _allreduce(self, x):
@@ -187,40 +189,56 @@ class SparseLlama:
 
     def _step_body(self, token: torch.Tensor, dev_state: bool) -> torch.Tensor:
         """One decode step for token ids [B].  With dev_state the position and the window length are
-        read from device tensors (and advanced on the device), so the launch sequence can be captured
-        in a CUDA graph and replayed; otherwise they are the host counters."""
+        read from a device tensor (and advanced on the device), so the launch sequence can be captured
+        in a CUDA graph and replayed; otherwise they are the host counters.  The dense comparison arm
+        (sparse=False) is plain torch: fp32 attention over the pruned tensors."""
+        if self.sparse:
+            return self._step_body_fused(token, dev_state)
         B = self.B
         x = self.embed[token].view(B, 1, -1)
-        hint = self._hint() if self.sparse else 0
-        w = self.wlen
-        pos = self._pos_dev if dev_state else torch.tensor([self.tokens], device=self.dev)
+        pos = torch.tensor([self.tokens], device=self.dev)
+        t = self.tokens
         for L in self.layers:
             h = _rms(x, L.n1, self.s.rms_eps)
             q, k, v = self._qkv(L, h, pos)
-            kf, vf = k.reshape(B * self.hkv, D), v.reshape(B * self.hkv, D)
-            if self.sparse and dev_state:
-                L.kwin.index_copy_(1, self._widx_dev, kf.unsqueeze(1))
-                L.vwin.index_copy_(1, self._widx_dev, vf.unsqueeze(1))
-                att = ops.decode_attention(q.reshape(B * self.hq, D), L.ks, L.vs, L.kwin, L.vwin, self.G,
-                                           stage_halves=hint, window_len=self._wlen_dev)
-            elif self.sparse:
-                L.kwin[:, w], L.vwin[:, w] = kf, vf
-                att = ops.decode_attention(q.reshape(B * self.hq, D), L.ks, L.vs, L.kwin[:, :w + 1], L.vwin[:, :w + 1],
-                                           self.G, stage_halves=hint)
-            else:
-                t = self.tokens
-                L.ks[:, t], L.vs[:, t] = kf, vf
-                kk = L.ks[:, :t + 1].float().repeat_interleave(self.G, dim=0)
-                vv = L.vs[:, :t + 1].float().repeat_interleave(self.G, dim=0)
-                sc = torch.bmm(kk, q.reshape(B * self.hq, D, 1).float()).squeeze(-1) / math.sqrt(D)
-                att = torch.bmm(torch.softmax(sc, -1).unsqueeze(1), vv).squeeze(1).half()
+            L.ks[:, t], L.vs[:, t] = k.reshape(B * self.hkv, D), v.reshape(B * self.hkv, D)
+            kk = L.ks[:, :t + 1].float().repeat_interleave(self.G, dim=0)
+            vv = L.vs[:, :t + 1].float().repeat_interleave(self.G, dim=0)
+            sc = torch.bmm(kk, q.reshape(B * self.hq, D, 1).float()).squeeze(-1) / math.sqrt(D)
+            att = torch.bmm(torch.softmax(sc, -1).unsqueeze(1), vv).squeeze(1).half()
             x = x + self._allreduce(F.linear(att.view(B, 1, self.hq * D), L.wo))
             x = x + self._mlp(L, _rms(x, L.n2, self.s.rms_eps))
-        if dev_state:
-            self._pos_dev += 1
-            self._widx_dev += 1
-            self._wlen_dev += 1
         return self._logits(x[:, 0])
+
+    def _step_body_fused(self, token: torch.Tensor, dev_state: bool) -> torch.Tensor:
+        """The sparse-cache step with the glue fused (step_ops): per layer RMSNorm(+residual add), q|k|v GEMM,
+        RoPE + window append, sparse attention, o_proj, RMSNorm(+add), gate|up GEMM, SiLU*up, down GEMM."""
+        B, eps = self.B, self.s.rms_eps
+        if self._inv_freq is None:
+            self._inv_freq = step_ops.rope_inv_freq(self.s.rope_theta, self.dev)
+            self._qbuf = torch.empty(B * self.hq, D, dtype=torch.float16, device=self.dev)
+        hint = self._hint()
+        w = self.wlen
+        x = self.embed[token]                     # [B, hidden], updated in place from here on
+        delta = None
+        for L in self.layers:
+            h = step_ops.add_rmsnorm(x, delta, L.n1, eps)
+            qkv = F.linear(h, L.wqkv)
+            if dev_state:
+                step_ops.rope_append(qkv, self._inv_freq, self._state[0:1], self._state[1:2], self.hq, self.hkv,
+                                     self._qbuf, L.kwin, L.vwin)
+                att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin, L.vwin, self.G, stage_halves=hint,
+                                           window_len=self._state[2:3])
+            else:
+                step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin)
+                att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G,
+                                           stage_halves=hint)
+            o = self._allreduce(F.linear(att.view(B, self.hq * D), L.wo))
+            h = step_ops.add_rmsnorm(x, o, L.n2, eps)
+            delta = self._allreduce(F.linear(step_ops.silu_mul(F.linear(h, L.wgu)), L.wd))
+        if dev_state:
+            self._state += 1
+        return F.linear(step_ops.add_rmsnorm(x, delta, self.norm, eps), self.lm_head)
 
     def _advance(self):
         self.tokens += 1
@@ -245,9 +263,8 @@ class SparseLlama:
                 out = self._step_body(token, False)       # sizes workspaces, resolves the stage hint
                 self._advance()
                 return out
-            self._pos_dev = torch.tensor([self.tokens], device=self.dev)
-            self._widx_dev = torch.tensor([self.wlen], device=self.dev)
-            self._wlen_dev = torch.tensor([self.wlen + 1], device=self.dev, dtype=torch.int32)
+            # position, window slot of the new token, window length: read on the device by the captured kernels
+            self._state = torch.tensor([self.tokens, self.wlen, self.wlen + 1], device=self.dev, dtype=torch.int32)
             self._tok_buf = token.clone()
             self._hint()
             torch.cuda.synchronize()

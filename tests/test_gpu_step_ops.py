@@ -1,0 +1,88 @@
+"""Fused decode-step glue kernels against the torch expressions they replace (same rounding steps)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rms_ref(x, w, eps):
+    v = x.float()
+    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype) * w
+
+
+def _rope_ref(x, pos, theta):
+    half = x.shape[-1] // 2
+    inv = 1.0 / (theta ** (torch.arange(0, half, device=x.device, dtype=torch.float32) / half))
+    ang = pos.float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().to(x.dtype), ang.sin().to(x.dtype)
+    x1, x2 = x[..., :half], x[..., half:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+
+@pytest.mark.parametrize("rows,hidden", [(1, 256), (32, 4096), (5, 1024)])
+def test_add_rmsnorm(rows, hidden):
+    from mustafar_b200 import step_ops
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(rows, hidden, generator=g, device="cuda").half()
+    d = torch.randn(rows, hidden, generator=g, device="cuda").half()
+    w = (1 + 0.1 * torch.randn(hidden, generator=g, device="cuda")).half()
+    x0 = x.clone()
+    out = step_ops.add_rmsnorm(x, None, w, 1e-5)
+    assert torch.equal(x, x0)
+    ref = _rms_ref(x0, w, 1e-5)
+    # the sum of squares is taken in another order: at most an fp16 ulp on a few elements
+    assert (out.float() - ref.float()).abs().max() <= 2e-3 * ref.float().abs().max()
+    assert (out != ref).float().mean() < 0.01
+    out2 = step_ops.add_rmsnorm(x, d, w, 1e-5)
+    assert torch.equal(x, x0 + d)
+    ref2 = _rms_ref(x0 + d, w, 1e-5)
+    assert (out2 != ref2).float().mean() < 0.01
+
+
+@pytest.mark.parametrize("dev_state", [False, True])
+def test_rope_append(dev_state):
+    from mustafar_b200 import step_ops
+    B, hq, hkv, cap, theta = 3, 8, 2, 16, 500000.0
+    g = torch.Generator(device="cuda").manual_seed(2)
+    qkv = torch.randn(B, (hq + 2 * hkv) * 128, generator=g, device="cuda").half()
+    kwin = torch.zeros(B * hkv, cap, 128, dtype=torch.float16, device="cuda")
+    vwin = torch.zeros_like(kwin)
+    q_out = torch.empty(B * hq, 128, dtype=torch.float16, device="cuda")
+    pos, slot = 4321, 7
+    inv = step_ops.rope_inv_freq(theta, "cuda")
+    if dev_state:
+        st = torch.tensor([pos, slot], dtype=torch.int32, device="cuda")
+        step_ops.rope_append(qkv, inv, st[0:1], st[1:2], hq, hkv, q_out, kwin, vwin)
+    else:
+        step_ops.rope_append(qkv, inv, pos, slot, hq, hkv, q_out, kwin, vwin)
+    q, k, v = qkv.split([hq * 128, hkv * 128, hkv * 128], dim=-1)
+    p = torch.tensor([pos], device="cuda")
+    q_ref = _rope_ref(q.view(B, 1, hq, 128).transpose(1, 2), p, theta).reshape(B * hq, 128)
+    k_ref = _rope_ref(k.view(B, 1, hkv, 128).transpose(1, 2), p, theta).reshape(B * hkv, 128)
+    # cosf / sinf may differ from torch's by an fp32 ulp, which shows after rounding on a few elements only
+    for got, ref in ((q_out, q_ref), (kwin[:, slot], k_ref)):
+        assert (got != ref).float().mean() < 0.01
+        assert (got.float() - ref.float()).abs().max() < 1e-2
+    assert torch.equal(vwin[:, slot], v.reshape(B * hkv, 128))
+    mask = torch.ones(cap, dtype=torch.bool)
+    mask[slot] = False
+    assert kwin[:, mask].abs().sum() == 0 and vwin[:, mask].abs().sum() == 0
+
+
+def test_silu_mul():
+    from mustafar_b200 import step_ops
+    g = torch.Generator(device="cuda").manual_seed(3)
+    gu = (3 * torch.randn(7, 2 * 1434, generator=g, device="cuda")).half()
+    out = step_ops.silu_mul(gu)
+    ref = torch.nn.functional.silu(gu[:, :1434]) * gu[:, 1434:]
+    assert (out != ref).float().mean() < 0.01
+    assert (out.float() - ref.float()).abs().max() <= 2e-3 * ref.float().abs().max()
+
+
+def test_argument_errors():
+    from mustafar_b200 import step_ops
+    x = torch.zeros(2, 100, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError):
+        step_ops.add_rmsnorm(x, None, torch.ones(100, dtype=torch.float16, device="cuda"), 1e-5)   # hidden % 8
+    with pytest.raises(RuntimeError):
+        step_ops.add_rmsnorm(x.float(), None, torch.ones(100, dtype=torch.float16, device="cuda"), 1e-5)
