@@ -58,17 +58,25 @@ def main():
     e[0].record()
     nxt = model.prefill(toks).argmax(-1)
     e[1].record()
+    marks = []
     for _ in range(a.new - 1):
         nxt = model.decode_step(nxt, graph=not a.no_graph).argmax(-1)
+        marks.append(torch.cuda.Event(enable_timing=True))
+        marks[-1].record()
     e[2].record()
     torch.cuda.synchronize()
+    # per-step device time: the median leaves out the steps that append a block or re-capture the graph
+    gaps = sorted(x.elapsed_time(y) for x, y in zip(marks[:-1], marks[1:]))
+    steady_ms = max_over_ranks(gaps[len(gaps) // 2], dist, dev) if gaps else 0.0
+    slowest_ms = max_over_ranks(gaps[-1], dist, dev) if gaps else 0.0
     prefill_ms = max_over_ranks(e[0].elapsed_time(e[1]), dist, dev)
     decode_ms = max_over_ranks(e[1].elapsed_time(e[2]), dist, dev)
     seqs = a.batch * (1 if tp > 1 else world)
     if rank == 0:
         print(json.dumps({
             "metric": "llama3_8b_shape_decode_throughput", "unit": "tok/s", "n_gpus": world,
-            "value": seqs * (a.new - 1) / (decode_ms * 1e-3), "tpot_ms": decode_ms / (a.new - 1), "ttft_ms": prefill_ms,
+            "value": seqs * (a.new - 1) / (decode_ms * 1e-3), "tpot_ms": decode_ms / (a.new - 1), "tpot_median_ms": steady_ms,
+            "slowest_step_ms": slowest_ms, "ttft_ms": prefill_ms,
             "config": {"workload": f"Llama-3-8B shape, {a.layers} layers, prompt {a.prompt}, {a.new} new tokens, "
                                    f"batch {a.batch} per {'job' if tp > 1 else 'GPU'}, sparsity {a.sparsity}, window 128",
                        "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}", "cache": "dense-pruned torch" if a.dense else "sparse fp16",
