@@ -223,4 +223,39 @@ int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G,
                          int64_t win_hs, int64_t win_ts, int W, const int* W_dev, float softmax_scale, float* ws,
                          int rec_index, unsigned* dev_status, cudaStream_t s);
 
+// Split count of the 64-token-block decode kernels.  The grid is n_kv_heads * ns CTAs of bps = ceil(nblk / ns) blocks.
+// The cost of a candidate follows a model fitted to a measured sweep of ns over batch 1..64 and
+// 4k..32k tokens on a B200 (all times in units of one block on an otherwise idle SM, ~2 us):
+//   * a CTA costs w = bps + 1.1 (prologue, partial record);
+//   * x = CTAs / 148 is the load per SM; an SM's throughput with o = min(x, 4) resident CTAs is
+//     rate(o) = 1 / 2 / 2.76 / 2.13 at o = 1 / 2 / 3 / 4, linear in between (the dip at 4 is the fit's
+//     way of saying that a grid which fits in one not-quite-full wave beats one that needs two);
+//   * the last, partly filled wave costs another 0.8 w once the SMs hold more than one CTA;
+//   * the combine kernel adds 0.035 per record.
+// The pick stays within 2 % of the best swept ns on every measured shape.
+inline int model_split_count(int n_kv_heads, int nblk, int min_ns, int max_ns) {
+    if (max_ns > nblk) max_ns = nblk;
+    if (min_ns < 1) min_ns = 1;
+    int ns = min_ns;
+    double best = -1.0;
+    for (int cand = min_ns; cand <= max_ns; ++cand) {
+        const int bps = (nblk + cand - 1) / cand;
+        const int real = (nblk + bps - 1) / bps;
+        const double x = static_cast<double>(n_kv_heads) * real / 148.0;
+        const double w = bps + 1.1;
+        double cost = w;
+        if (x > 1.0) {
+            const double o = x < 4.0 ? x : 4.0;
+            const double rate = o < 2.0 ? o : (o < 3.0 ? 2.0 + 0.76 * (o - 2.0) : 2.76 - 0.63 * (o - 3.0));
+            cost = x * w / rate + 0.8 * w * (x - 1.0 < 1.0 ? x - 1.0 : 1.0);
+        }
+        cost += 0.035 * real;
+        if (best < 0 || cost < best) {
+            best = cost;
+            ns = real;
+        }
+    }
+    return ns;
+}
+
 }  // namespace mfar

@@ -385,9 +385,8 @@ static int check_q(const void* bmp, const void* off, const void* sc, const void*
 }
 
 static void q_split(int n_kv_heads, int nblk, int hint, int* ns, int* bps) {
-    int n = hint > 0 ? hint : (148 * 8 + n_kv_heads - 1) / n_kv_heads;
-    const int max_n = (nblk + 1) / 2;
-    if (hint <= 0 && n > max_n) n = max_n;
+    const int max_n = (nblk + 1) / 2;   // what callers size their workspace for
+    int n = hint > 0 ? hint : model_split_count(n_kv_heads, nblk, 1, max_n < 128 ? max_n : 128);
     if (n > nblk) n = nblk;
     if (n < 1) n = 1;
     *bps = (nblk + n - 1) / n;
