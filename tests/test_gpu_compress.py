@@ -157,3 +157,26 @@ def test_full_size_properties(mod, sparsity):
         want_sum = (torch.where(nz, want, torch.zeros_like(want)).view(torch.int16).to(torch.int64) & 0xffff).sum()
         assert int(got_sum) == int(want_sum)
         del store
+
+
+def test_wire_format_round_trip_feeds_decode():
+    """A cache that went through the wire format (device -> blob -> device) decodes to the same output."""
+    import torch
+    from mustafar_b200 import compression as comp, ops, wire
+    g = torch.Generator(device="cuda").manual_seed(11)
+    Bh, L, G = 4, 512, 4
+    k = torch.randn(Bh, L, 128, generator=g, device="cuda").half()
+    v = torch.randn(Bh, L, 128, generator=g, device="cuda").half()
+    q = torch.randn(Bh * G, 128, generator=g, device="cuda").half()
+    ks, vs = comp.SparseStore(Bh, L, comp.KEY, "cuda"), comp.SparseStore(Bh, L, comp.VALUE, "cuda")
+    ks.append(k, comp.keep_rank(0.7))
+    vs.append(v, comp.keep_rank(0.7))
+    ks2 = wire.unpack_store(wire.pack_store(ks), "cuda", max_tokens=1024, nz_capacity=1024 * 64)
+    vs2 = wire.unpack_store(wire.pack_store(vs), "cuda", max_tokens=1024, nz_capacity=1024 * 64)
+    a = ops.decode_attention(q, ks, vs, None, None, G)
+    b = ops.decode_attention(q, ks2, vs2, None, None, G)
+    assert torch.equal(a, b)
+    # and the restored arena takes further appends
+    ks2.append(k[:, :64], comp.keep_rank(0.7))
+    assert ks2.tokens == L + 64
+    ks2.check()
