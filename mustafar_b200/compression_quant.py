@@ -47,6 +47,68 @@ def compress_quant(x: torch.Tensor, kind: int, prune_rank: int = 0, bits: int = 
                 units=units, scales=scales, zeros=zeros)
 
 
+class QuantStore:
+    """Arena for the quantised format: the seven arrays of ``compress_quant`` with room for ``max_tokens``,
+    filled in place by ``append`` (what the reference does with seven ``torch.cat`` per tensor per layer every
+    256 steps, ``models/llama_mustafar_quant_kernel.py:305-345``).
+
+    Code words of head h live at ``packed[h, :head_tail[h]]``; ``tile_offsets`` index the flattened ``packed``
+    (the kernels reach every tile through them), so the decode ops take this store as they take a compact one."""
+
+    def __init__(self, n_heads: int, max_tokens: int, kind: int, device, bits: int = 2, group: int = 64,
+                 words_capacity: int | None = None):
+        assert max_tokens % 64 == 0 and kind in (KEY, VALUE) and bits in (2, 4) and group in (32, 64)
+        self.n_heads, self.max_tokens, self.kind, self.bits, self.group = n_heads, max_tokens, kind, bits, group
+        self.tiles_cap = 2 * max_tokens
+        ngrp = 64 // group
+        T = self.tiles_cap
+        self.words_capacity = T * (64 * bits // 32) if words_capacity is None else int(words_capacity)
+        shape = (n_heads, T) if ngrp == 1 else (n_heads, T, ngrp)
+        self.bitmaps = torch.empty((n_heads, T), dtype=torch.int64, device=device)
+        self.tile_offsets = torch.empty((n_heads, T), dtype=torch.int32, device=device)
+        self.counts = torch.empty((n_heads, T), dtype=torch.int32, device=device)
+        self.units = torch.empty((n_heads, T), dtype=torch.int32, device=device)
+        self.scales = torch.empty(shape, dtype=torch.float16, device=device)
+        self.zeros = torch.empty(shape, dtype=torch.float16, device=device)
+        self.packed = torch.empty((n_heads, self.words_capacity), dtype=torch.int32, device=device)
+        self.head_tail = torch.zeros(n_heads, dtype=torch.int32, device=device)
+        self.stats = torch.zeros(1, dtype=torch.int32, device=device)
+        self.tokens = 0
+        self._scratch = None
+
+    def append(self, x: torch.Tensor, prune_rank: int = 0) -> None:
+        """Prune (``prune_rank`` > 0), quantise and store ``x`` [n_heads, n, 128], n % 64 == 0, behind the tokens held."""
+        x = _check_input(x)
+        n = x.shape[1]
+        if x.shape[0] != self.n_heads:
+            raise RuntimeError("head count mismatch")
+        if self.tokens + n > self.max_tokens:
+            raise RuntimeError("QuantStore is full")
+        if n == 0:
+            return
+        need = _lib.lib().mfar_compress_scratch_bytes(self.n_heads, n)
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(need, dtype=torch.uint8, device=self.bitmaps.device)
+        T = self.tiles_cap
+        st = _lib.lib().mfar_compress_quant(
+            x.data_ptr(), x.stride(0), x.stride(1), self.n_heads, n, self.kind, prune_rank, self.bits, self.group,
+            self.bitmaps.data_ptr(), T, self.tile_offsets.data_ptr(), self.counts.data_ptr(), self.units.data_ptr(),
+            self.scales.data_ptr(), self.zeros.data_ptr(), T, 2 * self.tokens, self.packed.data_ptr(),
+            self.words_capacity, self.words_capacity, self.head_tail.data_ptr(),
+            self._scratch.data_ptr(), self._scratch.numel(), self.stats.data_ptr(), _stream())
+        _lib.check(st, "mfar_compress_quant")
+        self.tokens += n
+
+    def check(self) -> None:
+        """Synchronises and raises if a kernel reported a device-side error (e.g. the code arena is full)."""
+        _lib.check_dev_status(int(self.stats[0].item()), "QuantStore")
+
+    def as_dict(self) -> dict:
+        """The arrays in the shape ``ops_quant.decode_attention_quant`` takes (no copies)."""
+        return dict(bitmaps=self.bitmaps, tile_offsets=self.tile_offsets, packed=self.packed.view(-1), counts=self.counts,
+                    units=self.units, scales=self.scales, zeros=self.zeros, head_stride=self.tiles_cap)
+
+
 def convert_key_batched_quant(inputs: torch.Tensor, return_metadata: bool = False):
     """Drop-in for ``kernel_quant/compression_quant.py:159-264``: inputs [B*Hkv, L, 128] (already
     pruned) -> (bitmaps, tile_offsets, packed, scales, zeros), with counts and units inserted

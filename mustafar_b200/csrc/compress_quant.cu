@@ -132,30 +132,14 @@ __global__ void __launch_bounds__(128) compress_quant_kernel(QuantParams p) {
     incl += wbase;
     const unsigned excl_tile = incl - units;
 
-    // chain: all blocks of all heads when the packed stream is compact, one chain per head otherwise
+    // chain: all blocks of all heads when the packed stream is compact, one chain per head otherwise.
+    // The block's total is announced now; the look-back itself waits until the codes are packed, by
+    // which time the predecessors have announced theirs.
     const bool compact = p.packed_hs == 0;
-    if (warp == 0) {
-        const int pos = h * p.nblk + b;
-        const long long e = lookback_exclusive(p.state, pos, compact ? 0 : h * p.nblk, total, p.err, p.dev_status);
-        if (lane == 0) s_excl = e;
-    }
-    __syncthreads();
-    if (s_excl < 0) return;
-
-    long long blk_start;   // uint32 offset in the flat packed buffer
-    long long limit;
-    if (compact) {
-        blk_start = s_excl;
-        limit = p.packed_cap;
-        if (p.head_tail && b == p.nblk - 1 && tid == 0) p.head_tail[h] = static_cast<int>(blk_start + total);
-    } else {
-        const long long tail = p.head_tail ? p.head_tail[h] : 0;
-        blk_start = h * p.packed_hs + tail + s_excl;
-        limit = h * p.packed_hs + p.packed_cap;
-    }
-
+    const int pos = h * p.nblk + b;
+    const int chain_first = compact ? 0 : h * p.nblk;
+    if (tid == 0) lookback_announce(p.state, pos, chain_first, total);
     p.bmp[h * p.bmp_hs + tile] = (static_cast<unsigned long long>(hi) << 32) | lo;
-    p.tile_off[mi] = static_cast<int>(blk_start + excl_tile);
     if (p.counts) p.counts[mi] = cnt;
     if (p.units) p.units[mi] = static_cast<int>(units);
 
@@ -178,9 +162,27 @@ __global__ void __launch_bounds__(128) compress_quant_kernel(QuantParams p) {
         }
         if (k % cap) ps[o++] = word;
     }
+    if (warp == 0) {
+        const long long e = lookback_exclusive(p.state, pos, chain_first, total, p.err, p.dev_status, false);
+        if (lane == 0) s_excl = e;
+    }
     __syncthreads();
-    // (in arena mode head_tail[h] is bumped by quant_bump_tails after this kernel, so every
-    // block of the head reads the same, old, tail)
+    if (s_excl < 0) return;
+
+    long long blk_start;   // uint32 offset in the flat packed buffer
+    long long limit;
+    if (compact) {
+        blk_start = s_excl;
+        limit = p.packed_cap;
+        if (p.head_tail && b == p.nblk - 1 && tid == 0) p.head_tail[h] = static_cast<int>(blk_start + total);
+    } else {
+        // (in arena mode head_tail[h] is bumped by quant_bump_tails after this kernel, so every
+        // block of the head reads the same, old, tail)
+        const long long tail = p.head_tail ? p.head_tail[h] : 0;
+        blk_start = h * p.packed_hs + tail + s_excl;
+        limit = h * p.packed_hs + p.packed_cap;
+    }
+    p.tile_off[mi] = static_cast<int>(blk_start + excl_tile);
     if (blk_start + total > limit) {
         if (tid == 0 && p.dev_status) atomicOr(p.dev_status, MFAR_DEV_CAPACITY);
         return;

@@ -14,6 +14,7 @@ import json
 
 import torch
 
+from . import _lib
 from . import compression as comp
 from . import compression_quant as cq
 from . import ops, ops_quant
@@ -126,6 +127,23 @@ def bench_compress_fp16(quick):
             y = torch.empty_like(x)
             us = timed(lambda: comp.prune(x, 0.7, out=y), iters=3, warmup=1)
             emit("prune only", us, 2 * x.numel() * 2, heads=Bh, tokens=L)
+        # the quantised kernel alone: outputs preallocated once, no host sync inside the timed calls
+        T, worst = 2 * L, Bh * 2 * L * 4
+        bufs = [torch.empty((Bh, T), dtype=dt, device="cuda") for dt in (torch.int64, torch.int32, torch.int32, torch.int32,
+                                                                          torch.float16, torch.float16)]
+        packed = torch.empty(worst, dtype=torch.int32, device="cuda")
+        info = torch.zeros(Bh + 1, dtype=torch.int32, device="cuda")
+        need = _lib.lib().mfar_compress_scratch_bytes(Bh, L)
+        scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+
+        def runq():
+            _lib.check(_lib.lib().mfar_compress_quant(
+                x.data_ptr(), x.stride(0), x.stride(1), Bh, L, kind, comp.keep_rank(0.7), 2, 64,
+                bufs[0].data_ptr(), T, bufs[1].data_ptr(), bufs[2].data_ptr(), bufs[3].data_ptr(), bufs[4].data_ptr(),
+                bufs[5].data_ptr(), T, 0, packed.data_ptr(), 0, worst, info.data_ptr(), scratch.data_ptr(), need,
+                info.data_ptr() + 4 * Bh, torch.cuda.current_stream().cuda_stream), "mfar_compress_quant")
+        us = timed(runq, iters=3, warmup=1)
+        emit(f"prune+compress {name} 2-bit (kernel only)", us, x.numel() * 2, heads=Bh, tokens=L, sparsity=0.7)
         del st, x
 
 

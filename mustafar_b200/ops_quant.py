@@ -147,14 +147,18 @@ def decode_attention_quant(q, kq: dict, vq: dict, n_tokens: int, k_window, v_win
     out = torch.empty((n_kv * group, D), dtype=torch.float16, device=q.device)
     ws = _workspace(q.device, n_kv * (max(1, n_tokens // 64) + 1) * group * 132 * 4)
     st = _dev_status(q.device)
-    qg = _qgroup(kq["scales"], n_kv, tiles) if n_tokens else 64
+    # compact tensors hold exactly `tiles` tiles per head; an arena (QuantStore.as_dict) says how far apart heads are
+    hs = int(kq.get("head_stride", tiles))
+    if int(vq.get("head_stride", tiles)) != hs:
+        raise RuntimeError("key and value tensors must share their head stride")
+    qg = _qgroup(kq["scales"], n_kv, hs) if n_tokens else 64
     r = _lib.lib().mfar_decode_attention_quant(
         q.data_ptr(), q.stride(0), n_kv, group,
         kq["bitmaps"].data_ptr(), kq["tile_offsets"].data_ptr(), kq["scales"].data_ptr(), kq["zeros"].data_ptr(),
         kq["packed"].data_ptr(), kq["packed"].numel(),
         vq["bitmaps"].data_ptr(), vq["tile_offsets"].data_ptr(), vq["scales"].data_ptr(), vq["zeros"].data_ptr(),
         vq["packed"].data_ptr(), vq["packed"].numel(),
-        tiles, tiles, n_tokens, bits, qg, kw, vw, wh, wt, W, float(softmax_scale), out.data_ptr(), out.stride(0),
+        hs, hs, n_tokens, bits, qg, kw, vw, wh, wt, W, float(softmax_scale), out.data_ptr(), out.stride(0),
         ws.data_ptr(), ws.numel(), nsplit, st.data_ptr(), _stream())
     _lib.check(r, "mfar_decode_attention_quant")
     if _debug_check():

@@ -126,3 +126,53 @@ def test_fused_quant_attention(m, G, Bh, L, W, s, bits, group):
     want = oracle.decode_attention_ref(q, kd, vd, kw, vw, G)
     out = m.oq.decode_attention_quant(q.cuda(), kq, vq, L, kw.cuda() if W else None, vw.cuda() if W else None, G, bits)
     assert oracle.rel_l2(out.float().cpu(), want) < TOL
+
+
+@pytest.mark.parametrize("kind", [0, 1])
+@pytest.mark.parametrize("bits,group", [(2, 64), (4, 64), (2, 32)])
+def test_quant_store_appends_match_one_shot_compression(m, kind, bits, group):
+    """Arena mode of mfar_compress_quant: three appends (256 + 64 + 192 tokens) leave, tile by tile, what one
+    call over all 512 tokens leaves in the compact layout; decode over the arena equals decode over the compact one."""
+    from mustafar_b200 import compression as comp
+    from mustafar_b200 import compression_quant as cq
+    Bh, L, G = 4, 512, 4
+    k, v = oracle.make_kv(Bh, L, seed=91 + kind)
+    x = (k if kind == 0 else v).cuda()
+    rank = comp.keep_rank(0.7)
+    ref = cq.compress_quant(x, kind, rank, bits, group)
+    st = cq.QuantStore(Bh, 1024, kind, "cuda", bits, group)
+    for a, b in ((0, 256), (256, 320), (320, 512)):
+        st.append(x[:, a:b], rank)
+    st.check()
+    T = 2 * L
+    d = st.as_dict()
+    assert st.tokens == L
+    assert torch.equal(d["bitmaps"][:, :T], ref["bitmaps"])
+    assert torch.equal(d["counts"][:, :T], ref["counts"]) and torch.equal(d["units"][:, :T], ref["units"])
+    assert torch.equal(d["scales"][:, :T], ref["scales"]) and torch.equal(d["zeros"][:, :T], ref["zeros"])
+    # same code words tile by tile (the offsets differ: per-head arena vs one flat stream)
+    offs_a, offs_r, units = d["tile_offsets"][:, :T].cpu(), ref["tile_offsets"].cpu(), ref["units"].cpu()
+    flat_a, flat_r = d["packed"].cpu(), ref["packed"].cpu()
+    for h in range(Bh):
+        for t in range(0, T, 37):
+            n = int(units[h, t])
+            assert torch.equal(flat_a[offs_a[h, t]:offs_a[h, t] + n], flat_r[offs_r[h, t]:offs_r[h, t] + n])
+    assert (st.head_tail.cpu() == units.sum(1).to(torch.int32)).all()
+    if kind == 0:
+        vs = cq.QuantStore(Bh, 1024, 1, "cuda", bits, group)
+        vs.append(v.cuda(), rank)
+        vref = cq.compress_quant(v.cuda(), 1, rank, bits, group)
+        q = oracle.make_query(Bh * G, seed=5).cuda()
+        a = m.oq.decode_attention_quant(q, d, vs.as_dict(), L, None, None, G, bits)
+        b = m.oq.decode_attention_quant(q, ref, vref, L, None, None, G, bits)
+        assert torch.equal(a, b)
+
+
+def test_quant_store_reports_a_full_code_arena(m):
+    from mustafar_b200 import compression_quant as cq
+    from mustafar_b200._lib import MustafarError
+    k, _ = oracle.make_kv(2, 128, seed=7)
+    st = cq.QuantStore(2, 128, 0, "cuda", words_capacity=64)     # far too small
+    st.append(k.cuda(), 0)
+    with pytest.raises(MustafarError):
+        st.check()
