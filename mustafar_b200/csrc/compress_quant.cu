@@ -1,14 +1,16 @@
 // Fused per-token magnitude prune + bitmap + asymmetric low-bit quantised compression.
 //
-// Same skeleton as compress.cu (one CTA of 128 threads per 64-token block of one head, rows
-// pruned in registers by thread pairs, one thread per tile afterwards, decoupled look-back for
-// the block's position in the packed stream).  Per tile the thread makes two passes over its
-// 64 values in shared memory:
-//   pass 1  bitmap, raw count, min / max of the nonzeros of every group
-//           -> scale = (max - min) / (2^bits - 1) (1 if that is 0), zero = floor(-min / scale + 0.5),
-//              both computed in fp32 and stored fp16;
-//   pass 2  codes clamp(floor(v / scale_fp16 + 0.5) + zero_fp16, 0, 2^bits - 1), IEEE division,
-//           packed 32/bits per uint32, least significant first.
+// Same skeleton as compress.cu (one CTA of 128 threads per 64-token block of one head, the row
+// selection leaves one "kept and nonzero" flag per element, the flags become the bitmaps, decoupled
+// look-back for the block's position in the packed stream).  Then:
+//   1. the kept values go to shared memory in tile order, unpadded;
+//   2. one thread per tile takes min / max of every group of its values
+//      -> scale = (max - min) / (2^bits - 1) (1 if that is 0), zero = floor(-min / scale + 0.5),
+//         both computed in fp32 and stored fp16;
+//   3. the block's values are dealt out evenly over the threads (tiles differ wildly in size: a K
+//      outlier channel keeps all 64 tokens, most keep ~20), each computes
+//      clamp(floor(v / scale_fp16 + 0.5) + zero_fp16, 0, 2^bits - 1), IEEE division, and ors its
+//      code into the tile's word: 32/bits codes per uint32, least significant first.
 // bits = 2, group = 64 reproduces kernel_quant/compression_quant.py bit for bit; bits = 4 and
 // group = 32 (a fresh scale / zero every 32 nonzeros of a tile) extend it.
 #include "compress_common.cuh"
@@ -58,79 +60,107 @@ __device__ __forceinline__ GroupQ make_group(float xmin, float xmax, bool has, i
 
 template <int KIND>
 __global__ void __launch_bounds__(128) compress_quant_kernel(QuantParams p) {
-    __shared__ __align__(16) unsigned short xs[64 * kXsStride];
-    __shared__ unsigned ps[128 * 8];
-    __shared__ unsigned s_warp[4];
+    __shared__ __align__(16) unsigned short vals[64 * 128];                                     // kept values, tile order, no padding
+    __shared__ __align__(16) unsigned short xs[KIND == MFAR_KIND_KEY ? 64 * kXsStride : 8];     // K: the raw block
+    __shared__ unsigned s_mask[4][64];       // K: keep flags [32-channel word][row], first channel in the top bit
+    __shared__ unsigned s_voff[129];         // first value of every tile in vals (and the total)
+    __shared__ unsigned s_woff[129];         // first code word of every tile in words (and the total)
+    __shared__ float4 s_par[128];            // per tile: scale, zero of group 0, scale, zero of group 1 (fp16 values, widened)
+    __shared__ unsigned words[128 * 8];      // code words of the block, final order
+    __shared__ unsigned s_warp[4][2];
     __shared__ unsigned s_ticket;
     __shared__ long long s_excl;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
+    const int r = tid >> 1, hh = tid & 1;    // row of the block and member of the pair that owns it
     if (tid == 0) s_ticket = atomicAdd(p.ticket, 1u);
     __syncthreads();
     const int h = static_cast<int>(s_ticket) / p.nblk;
     const int b = static_cast<int>(s_ticket) % p.nblk;
     if (h >= p.n_heads) return;
-
-    {
-        const int r = tid >> 1, hh = tid & 1;
-        uint4 v[8];
-        load_prune_row(p.x + h * p.xhs + (static_cast<int64_t>(b) * 64 + r) * p.xts, hh, p.rank, false, v);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(&xs[r * kXsStride + 8 * (2 * j + hh)]) = v[j];
-    }
-    __syncthreads();
-
-    // element e of this thread's tile
-    const int base = (KIND == MFAR_KIND_KEY) ? tid : ((tid & 63) * kXsStride + (tid >> 6) * 64);
-    const int step = (KIND == MFAR_KIND_KEY) ? kXsStride : 1;
     const int maxq = (1 << p.bits) - 1;
     const int cap = 32 / p.bits;
     const int ngrp = 64 / p.group;
 
-    // ---- pass 1
-    unsigned hi = 0, lo = 0;
-    int cnt = 0;
-    float mn[2] = {INFINITY, INFINITY}, mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll 8
-    for (int e = 0; e < 64; ++e) {
-        const unsigned short u = xs[base + e * step];
-        const bool nz = (u & 0x7fffu) != 0;
-        if (e < 32) hi = (hi << 1) | nz; else lo = (lo << 1) | nz;
-        if (nz) {
-            const float f = __half2float(__ushort_as_half(u));
-            const int g = (ngrp == 2 && cnt >= 32) ? 1 : 0;
-            mn[g] = fminf(mn[g], f);
-            mx[g] = fmaxf(mx[g], f);
-            ++cnt;
-        }
-    }
-    const int64_t tile = p.tile_start + static_cast<int64_t>(b) * kTilesPerBlock + tid;
-    const int64_t mi = h * p.meta_hs + tile;
-    GroupQ gq[2];
-    for (int g = 0; g < ngrp; ++g)
-        gq[g] = make_group(mn[g], mx[g], cnt > 32 * g, maxq, &p.scales[mi * ngrp + g], &p.zeros[mi * ngrp + g]);
-    const unsigned units = (cnt + cap - 1) / cap;
-
-    // ---- scan of the units, position of the block in the packed stream
-    unsigned incl = units;
+    // ---- the pair loads one row, selects the threshold, ends up with one "kept and nonzero" flag per element
+    uint4 v[8];
+    {
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + h * p.xhs + (static_cast<int64_t>(b) * 64 + r) * p.xts);
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
+        for (int j = 0; j < 8; ++j) v[j] = ldg_nc_u4(src + 2 * j + hh);
+    }
+    const unsigned (&w)[32] = reinterpret_cast<const unsigned (&)[32]>(v);
+    if (KIND == MFAR_KIND_KEY) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) *reinterpret_cast<uint4*>(&xs[r * kXsStride + 8 * (2 * j + hh)]) = v[j];
+    }
+    const RowSelect sel = select_row(w, p.rank);
+    const unsigned y0 = plane_to_bitmap_order(sel.keep0), y1 = plane_to_bitmap_order(sel.keep1);
+    const unsigned q0 = __shfl_xor_sync(kFull, y0, 1), q1 = __shfl_xor_sync(kFull, y1, 1);
+    unsigned hi0, lo0, hi1, lo1;
+    interleave_chunk_bytes(hh ? q0 : y0, hh ? y0 : q0, hi0, lo0);   // channels 0..63
+    interleave_chunk_bytes(hh ? q1 : y1, hh ? y1 : q1, hi1, lo1);   // channels 64..127
+#pragma unroll
+    for (int j = 0; j < 8; ++j) words[tid + 128 * j] = 0;
+
+    // ---- bitmap, count and code words of the tile this thread answers for; both running sums in one scan
+    // (values in the low half, words in the high half: at most 8192 and 1024 per block)
+    unsigned hi, lo;
+    int tile;
+    if (KIND == MFAR_KIND_KEY) {
+        if (hh == 0) {
+            s_mask[0][r] = hi0;
+            s_mask[1][r] = lo0;
+        } else {
+            s_mask[2][r] = hi1;
+            s_mask[3][r] = lo1;
+        }
+        __syncthreads();
+        hi = __brev(warp_transpose32(__brev(s_mask[warp][lane])));
+        lo = __brev(warp_transpose32(__brev(s_mask[warp][32 + lane])));
+        tile = tid;
+    } else {
+        hi = hh ? hi1 : hi0;
+        lo = hh ? lo1 : lo0;
+        tile = hh * 64 + r;
+    }
+    const int cnt = __popc(hi) + __popc(lo);
+    const unsigned units = (cnt + cap - 1) / cap;
+    const unsigned both = static_cast<unsigned>(cnt) | (units << 16);
+    unsigned incl = both;
+#pragma unroll
+    for (int d = (KIND == MFAR_KIND_KEY ? 1 : 2); d < 32; d <<= 1) {
         const unsigned n = __shfl_up_sync(kFull, incl, d);
         if (lane >= d) incl += n;
     }
-    if (lane == 31) s_warp[warp] = incl;
-    __syncthreads();
-    unsigned wbase = 0, total = 0;
-#pragma unroll
-    for (int w = 0; w < 4; ++w) {
-        const unsigned t = s_warp[w];
-        if (w < warp) wbase += t;
-        total += t;
+    if (KIND == MFAR_KIND_KEY) {
+        if (lane == 31) s_warp[warp][0] = incl;
+    } else if (lane >= 30) {
+        s_warp[warp][hh] = incl;
     }
-    incl += wbase;
-    const unsigned excl_tile = incl - units;
+    __syncthreads();
+    unsigned all = 0;
+    {
+        unsigned half0 = 0;
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+            const unsigned t0 = s_warp[wi][0], t1 = (KIND == MFAR_KIND_KEY) ? 0u : s_warp[wi][1];
+            if (wi < warp) incl += (KIND == MFAR_KIND_VALUE && hh) ? t1 : t0;
+            half0 += t0;
+            all += t0 + t1;
+        }
+        if (KIND == MFAR_KIND_VALUE && hh) incl += half0;   // all of channel half 0 comes before half 1
+    }
+    const unsigned excl = incl - both;
+    const unsigned voff = excl & 0xffffu, woff = excl >> 16;
+    const unsigned total_vals = all & 0xffffu, total = all >> 16;
+    s_voff[tile] = voff;
+    s_woff[tile] = woff;
+    if (tid == 0) {
+        s_voff[128] = total_vals;
+        s_woff[128] = total;
+    }
 
     // chain: all blocks of all heads when the packed stream is compact, one chain per head otherwise.
     // The block's total is announced now; the look-back itself waits until the codes are packed, by
@@ -139,29 +169,94 @@ __global__ void __launch_bounds__(128) compress_quant_kernel(QuantParams p) {
     const int pos = h * p.nblk + b;
     const int chain_first = compact ? 0 : h * p.nblk;
     if (tid == 0) lookback_announce(p.state, pos, chain_first, total);
-    p.bmp[h * p.bmp_hs + tile] = (static_cast<unsigned long long>(hi) << 32) | lo;
-    if (p.counts) p.counts[mi] = cnt;
-    if (p.units) p.units[mi] = static_cast<int>(units);
 
-    // ---- pass 2: codes, packed in shared memory in final order
-    {
-        unsigned word = 0, o = excl_tile;
-        int k = 0;
+    // ---- kept values into vals, tile order (K: down the columns of the raw block; V: from the registers)
+    if (KIND == MFAR_KIND_KEY) {
+        unsigned o = voff;
+        const int c = tid;
 #pragma unroll 8
-        for (int e = 0; e < 64; ++e) {
-            const unsigned short u = xs[base + e * step];
-            if ((u & 0x7fffu) != 0) {
-                const GroupQ& g = gq[(ngrp == 2 && k >= 32) ? 1 : 0];
-                const float f = __half2float(__ushort_as_half(u));
-                float q = __fadd_rn(floorf(__fadd_rn(__fdiv_rn(f, g.scale), 0.5f)), g.zero);
-                q = fminf(fmaxf(q, 0.f), static_cast<float>(maxq));
-                word |= static_cast<unsigned>(q) << ((k % cap) * p.bits);
-                ++k;
-                if (k % cap == 0) { ps[o++] = word; word = 0; }
+        for (int i = 0; i < 32; ++i)
+            if ((hi >> (31 - i)) & 1u) vals[o++] = xs[i * kXsStride + c];
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i)
+            if ((lo >> (31 - i)) & 1u) vals[o++] = xs[(32 + i) * kXsStride + c];
+    } else {
+        const unsigned voff_other = __shfl_xor_sync(kFull, voff, 1);
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+            const unsigned thi = t ? hi1 : hi0, tlo = t ? lo1 : lo0, y = t ? y1 : y0;
+            const unsigned long long bm = (static_cast<unsigned long long>(thi) << 32) | tlo;
+            const unsigned off = (hh == t) ? voff : voff_other;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int cidx = 2 * k + hh;                        // chunk inside the tile
+                unsigned o = off + (cidx ? __popcll(bm >> (64 - 8 * cidx)) : 0);
+                const unsigned flags = y >> (24 - 8 * k);           // bit 7 = first element of the chunk
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const unsigned word = w[16 * t + 4 * k + (e >> 1)];
+                    if ((flags >> (7 - e)) & 1u) vals[o++] = static_cast<unsigned short>((e & 1) ? (word >> 16) : word);
+                }
             }
         }
-        if (k % cap) ps[o++] = word;
     }
+    __syncthreads();
+
+    // ---- per tile: min / max of every group -> scale, zero (fp32 arithmetic, stored fp16).  One thread per
+    // tile; dealing the values out evenly with shared-memory min / max on ordered keys measured slower.
+    const int64_t gtile = p.tile_start + static_cast<int64_t>(b) * kTilesPerBlock + tile;
+    const int64_t mi = h * p.meta_hs + gtile;
+    {
+        float mn0 = INFINITY, mx0 = -INFINITY, mn1 = INFINITY, mx1 = -INFINITY;
+        const int n0 = (ngrp == 2 && cnt > 32) ? 32 : cnt;
+        for (int k = 0; k < n0; ++k) {
+            const float f = __half2float(__ushort_as_half(vals[voff + k]));
+            mn0 = fminf(mn0, f);
+            mx0 = fmaxf(mx0, f);
+        }
+        for (int k = n0; k < cnt; ++k) {
+            const float f = __half2float(__ushort_as_half(vals[voff + k]));
+            mn1 = fminf(mn1, f);
+            mx1 = fmaxf(mx1, f);
+        }
+        const GroupQ g0 = make_group(mn0, mx0, cnt > 0, maxq, &p.scales[mi * ngrp], &p.zeros[mi * ngrp]);
+        GroupQ g1;
+        g1.scale = 1.f;
+        g1.zero = 0.f;
+        if (ngrp == 2) g1 = make_group(mn1, mx1, cnt > 32, maxq, &p.scales[mi * 2 + 1], &p.zeros[mi * 2 + 1]);
+        s_par[tile] = make_float4(g0.scale, g0.zero, g1.scale, g1.zero);
+    }
+    __syncthreads();
+
+    // ---- codes: the block's values are dealt out evenly, a contiguous run per thread (tiles differ wildly in
+    // size: a K outlier channel keeps all 64 tokens, most keep ~20); each code is or-ed into its tile's word
+    {
+        const unsigned per = (total_vals + 127u) >> 7;
+        const unsigned run0 = tid * per, run1 = min(run0 + per, total_vals);
+        if (run0 < run1) {
+            int t = 0;   // tile of the first value: largest t with s_voff[t] <= run0
+#pragma unroll
+            for (int step = 64; step; step >>= 1)
+                if (t + step < 128 && s_voff[t + step] <= run0) t += step;
+            unsigned base_t = s_voff[t], next = s_voff[t + 1];
+            for (unsigned i = run0; i < run1; ++i) {
+                while (i >= next) {   // also skips empty tiles
+                    ++t;
+                    base_t = next;
+                    next = s_voff[t + 1];
+                }
+                const unsigned k = i - base_t;
+                const float4 par = s_par[t];
+                const bool g1 = (ngrp == 2 && k >= 32u);
+                const float scale = g1 ? par.z : par.x, zero = g1 ? par.w : par.y;
+                const float f = __half2float(__ushort_as_half(vals[i]));
+                float q = __fadd_rn(floorf(__fadd_rn(__fdiv_rn(f, scale), 0.5f)), zero);
+                q = fminf(fmaxf(q, 0.f), static_cast<float>(maxq));
+                atomicOr(&words[s_woff[t] + k / cap], static_cast<unsigned>(q) << ((k % cap) * p.bits));
+            }
+        }
+    }
+
     if (warp == 0) {
         const long long e = lookback_exclusive(p.state, pos, chain_first, total, p.err, p.dev_status, false);
         if (lane == 0) s_excl = e;
@@ -182,12 +277,15 @@ __global__ void __launch_bounds__(128) compress_quant_kernel(QuantParams p) {
         blk_start = h * p.packed_hs + tail + s_excl;
         limit = h * p.packed_hs + p.packed_cap;
     }
-    p.tile_off[mi] = static_cast<int>(blk_start + excl_tile);
+    p.bmp[h * p.bmp_hs + gtile] = (static_cast<unsigned long long>(hi) << 32) | lo;
+    p.tile_off[mi] = static_cast<int>(blk_start + woff);
+    if (p.counts) p.counts[mi] = cnt;
+    if (p.units) p.units[mi] = static_cast<int>(units);
     if (blk_start + total > limit) {
         if (tid == 0 && p.dev_status) atomicOr(p.dev_status, MFAR_DEV_CAPACITY);
         return;
     }
-    for (unsigned i = tid; i < total; i += 128) p.packed[blk_start + i] = ps[i];
+    for (unsigned i = tid; i < total; i += 128) p.packed[blk_start + i] = words[i];
 }
 
 // arena mode: head_tail[h] += words appended (separate tiny launch so that no block reads a moved tail)
