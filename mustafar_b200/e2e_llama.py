@@ -80,7 +80,7 @@ def main():
             "config": {"workload": f"Llama-3-8B shape, {a.layers} layers, prompt {a.prompt}, {a.new} new tokens, "
                                    f"batch {a.batch} per {'job' if tp > 1 else 'GPU'}, sparsity {a.sparsity}, window 128",
                        "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}", "cache": "dense-pruned torch" if a.dense else "sparse fp16",
-                       "cuda_graph": bool(not a.no_graph and not a.dense and tp == 1)},
+                       "cuda_graph": (False if (a.no_graph or a.dense) else ("one graph per stretch between collectives" if tp > 1 else True))},
             "data": "synthetic (random-init weights, random prompt ids)", "dtype": "f16"}))
     if dist is not None:
         dist.barrier()

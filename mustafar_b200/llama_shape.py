@@ -210,15 +210,21 @@ class SparseLlama:
             x = x + self._mlp(L, _rms(x, L.n2, self.s.rms_eps))
         return self._logits(x[:, 0])
 
-    def _step_body_fused(self, token: torch.Tensor, dev_state: bool) -> torch.Tensor:
+    def _step_segments(self, token: torch.Tensor, dev_state: bool):
         """The sparse-cache step with the glue fused (step_ops): per layer RMSNorm(+residual add), q|k|v GEMM,
-        RoPE + window append, sparse attention, o_proj, RMSNorm(+add), gate|up GEMM, SiLU*up, down GEMM."""
+        RoPE + window append, sparse attention, o_proj, RMSNorm(+add), gate|up GEMM, SiLU*up, down GEMM.
+
+        A generator: under tensor parallelism it yields every partial sum that needs an all-reduce (in place,
+        done by the caller) and resumes after it, so that the stretches between two collectives can each be
+        captured in a CUDA graph of their own while NCCL stays outside any capture.  The logits end up in
+        ``self._step_out``."""
         B, eps = self.B, self.s.rms_eps
         if self._inv_freq is None:
             self._inv_freq = step_ops.rope_inv_freq(self.s.rope_theta, self.dev)
             self._qbuf = torch.empty(B * self.hq, D, dtype=torch.float16, device=self.dev)
         hint = self._hint()
         w = self.wlen
+        tp = self.tp_world > 1
         x = self.embed[token]                     # [B, hidden], updated in place from here on
         delta = None
         for L in self.layers:
@@ -233,12 +239,49 @@ class SparseLlama:
                 step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin)
                 att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G,
                                            stage_halves=hint)
-            o = self._allreduce(F.linear(att.view(B, self.hq * D), L.wo))
+            o = F.linear(att.view(B, self.hq * D), L.wo)
+            if tp:
+                yield o
             h = step_ops.add_rmsnorm(x, o, L.n2, eps)
-            delta = self._allreduce(F.linear(step_ops.silu_mul(F.linear(h, L.wgu)), L.wd))
+            delta = F.linear(step_ops.silu_mul(F.linear(h, L.wgu)), L.wd)
+            if tp:
+                yield delta
         if dev_state:
             self._state += 1
-        return F.linear(step_ops.add_rmsnorm(x, delta, self.norm, eps), self.lm_head)
+        self._step_out = F.linear(step_ops.add_rmsnorm(x, delta, self.norm, eps), self.lm_head)
+
+    def _step_body_fused(self, token: torch.Tensor, dev_state: bool) -> torch.Tensor:
+        for partial in self._step_segments(token, dev_state):
+            self.dist.all_reduce(partial)
+        return self._step_out
+
+    def _capture_step(self):
+        """Captures the step as one CUDA graph per stretch between two collectives (a single graph without
+        tensor parallelism).  Returns [(graph, tensor to all-reduce after it or None)]; replay in order."""
+        # capture_begin / capture_end on a side stream, without the garbage collection and the allocator purge
+        # that `with torch.cuda.graph(...)` adds on entry: after a prefill the purge alone can take most of a second
+        pool = torch.cuda.graph_pool_handle()
+        gen = self._step_segments(self._tok_buf, True)
+        out = []
+        side = torch.cuda.Stream(device=self.dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            while True:
+                g = torch.cuda.CUDAGraph()
+                partial = None
+                g.capture_begin(pool=pool)
+                try:
+                    try:
+                        partial = next(gen)
+                    except StopIteration:
+                        pass
+                finally:
+                    g.capture_end()
+                out.append((g, partial))
+                if partial is None:
+                    break
+        torch.cuda.current_stream().wait_stream(side)
+        return out
 
     def _advance(self):
         self.tokens += 1
@@ -251,9 +294,10 @@ class SparseLlama:
     def decode_step(self, token: torch.Tensor, graph: bool = False) -> torch.Tensor:
         """token [B] (ids of the newest position) -> logits [B, vocab].
 
-        graph=True replays a CUDA graph of the step (re-captured after every 256-token block append,
-        because the compressed length is a launch argument); the first step of each epoch runs eagerly."""
-        if not (graph and self.sparse and self.tp_world == 1):    # NCCL collectives stay outside graph capture
+        graph=True replays CUDA graphs of the step (re-captured after every 256-token block append, because
+        the compressed length is a launch argument); the first step of each epoch runs eagerly.  Under tensor
+        parallelism the step is a chain of graphs with the NCCL all-reduces launched between them."""
+        if not (graph and self.sparse):
             out = self._step_body(token, False)
             self._advance()
             return out
@@ -268,13 +312,13 @@ class SparseLlama:
             self._tok_buf = token.clone()
             self._hint()
             torch.cuda.synchronize()
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                self._logits_buf = self._step_body(self._tok_buf, True)
-            self._graph = g
+            self._graph = self._capture_step()
         self._tok_buf.copy_(token)
-        self._graph.replay()
-        out = self._logits_buf
+        for g, partial in self._graph:
+            g.replay()
+            if partial is not None:
+                self.dist.all_reduce(partial)
+        out = self._step_out
         self._eager_done = False if self.wlen + 1 == self.wcap else self._eager_done
         self._advance()
         return out

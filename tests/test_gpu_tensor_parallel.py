@@ -12,8 +12,9 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_tp2_matches_single_gpu():
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+@pytest.mark.parametrize("graph", ["0", "1"])
+def test_tp2_matches_single_gpu(graph):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_WORKER_GRAPH=graph)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", "29661", os.path.join(HERE, "tp_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)

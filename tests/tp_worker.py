@@ -21,10 +21,12 @@ def main():
     ref = SparseLlama(shape, B, 1024, "cuda", seed=11) if rank == 0 else None
     lr = ref.prefill(toks) if rank == 0 else None
     worst = 0.0
+    use_graph = os.environ.get("TP_WORKER_GRAPH", "0") == "1"
     for i in range(12):
         nxt = lt.argmax(-1)
         dist.broadcast(nxt, 0)
-        lt = tp.decode_step(nxt)          # eager: collectives are not captured in CUDA graphs here
+        # graph: one CUDA graph per stretch between two collectives, the all-reduces launched eagerly in between
+        lt = tp.decode_step(nxt, graph=use_graph)
         if rank == 0:
             lr = ref.decode_step(nxt)
             err = float(torch.linalg.norm(lt.float() - lr.float()) / torch.linalg.norm(lr.float()))
