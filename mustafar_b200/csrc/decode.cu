@@ -31,7 +31,13 @@ constexpr int kThreads = kWarps * 32;
 #define MFAR_STAGES 2
 #endif
 constexpr int kStages = MFAR_STAGES;
-constexpr int kPlanes = kWarps * 4;          // K-phase partial planes: (warp, lane group)
+// K-phase partial planes: (warp, lane group), halved by every shuffle stage that folds two lane groups first
+#ifndef MFAR_PLANE_FOLD
+#define MFAR_PLANE_FOLD 1
+#endif
+constexpr int kPlaneFold = MFAR_PLANE_FOLD;                 // 0, 1 or 2
+constexpr int kGroupsPerWarp = 4 >> kPlaneFold;
+constexpr int kPlanes = kWarps * kGroupsPerWarp;
 constexpr int kMaxBlocksPerSplit = 256;
 
 // A stage holds, per staged tensor, 1 KiB of bitmaps and cap (+slack) packed halves;
@@ -278,12 +284,27 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
                     }
                 }
             }
-            // each (warp, group) owns a partial plane: spart[plane][g][8*kb .. 8*kb+7]
-            float* dst = spart + (static_cast<size_t>(warp * 4 + gi) * G) * 64 + kb * 8;
+            // fold lane groups (same tokens, other channels) by shuffles first when planes are to be saved
+            if (kPlaneFold >= 1) {
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                *reinterpret_cast<float4*>(dst + g * 64) = make_float4(acc_s[0][g], acc_s[1][g], acc_s[2][g], acc_s[3][g]);
-                *reinterpret_cast<float4*>(dst + g * 64 + 4) = make_float4(acc_s[4][g], acc_s[5][g], acc_s[6][g], acc_s[7][g]);
+                for (int t = 0; t < 8; ++t)
+#pragma unroll
+                    for (int g = 0; g < G; ++g) acc_s[t][g] += __shfl_xor_sync(kFull, acc_s[t][g], 16);
+            }
+            if (kPlaneFold >= 2) {
+#pragma unroll
+                for (int t = 0; t < 8; ++t)
+#pragma unroll
+                    for (int g = 0; g < G; ++g) acc_s[t][g] += __shfl_xor_sync(kFull, acc_s[t][g], 8);
+            }
+            // each (warp, remaining group) owns a partial plane: spart[plane][g][8*kb .. 8*kb+7]
+            if (gi < kGroupsPerWarp) {
+                float* dst = spart + (static_cast<size_t>(warp * kGroupsPerWarp + gi) * G) * 64 + kb * 8;
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    *reinterpret_cast<float4*>(dst + g * 64) = make_float4(acc_s[0][g], acc_s[1][g], acc_s[2][g], acc_s[3][g]);
+                    *reinterpret_cast<float4*>(dst + g * 64 + 4) = make_float4(acc_s[4][g], acc_s[5][g], acc_s[6][g], acc_s[7][g]);
+                }
             }
         }
         if (MODE != MODE_VALUE) MFAR_LOOP_SYNC();
