@@ -38,6 +38,7 @@ constexpr int kStages = MFAR_STAGES;
 constexpr int kPlaneFold = MFAR_PLANE_FOLD;                 // 0, 1 or 2
 constexpr int kGroupsPerWarp = 4 >> kPlaneFold;
 constexpr int kPlanes = kWarps * kGroupsPerWarp;
+static_assert(kPlanes * 64 >= kWarps * kD, "the epilogue reuses the score planes as [warp][G][128] floats");
 constexpr int kMaxBlocksPerSplit = 256;
 
 // A stage holds, per staged tensor, 1 KiB of bitmaps and cap (+slack) packed halves;

@@ -18,7 +18,8 @@ namespace mfar {
 
 constexpr int kQWarps = 4;
 constexpr int kQThreads = kQWarps * 32;
-constexpr int kQPlanes = kQWarps * 4;
+constexpr int kQPlanes = kQWarps * 2;   // (warp, pair of lane groups): two lane groups are folded by a shuffle first
+static_assert(kQPlanes * 64 >= kQWarps * kD, "the epilogue reuses the score planes as [warp][G][128] floats");
 
 struct QSparse {
     const unsigned long long* bmp;
@@ -226,11 +227,17 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
                 load_coef<G>(qh + c * G, coef);
                 tile_step_q<G, BITS, GROUP32>(bm.y, bm.x, kbf.words + c * WPT, kbf.sz + 2 * c, sel, mh, ml, coef, acc_s);
             }
-            float* dst = spart + (static_cast<size_t>(warp * 4 + gi) * G) * 64 + kb * 8;
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                *reinterpret_cast<float4*>(dst + g * 64) = make_float4(acc_s[0][g], acc_s[1][g], acc_s[2][g], acc_s[3][g]);
-                *reinterpret_cast<float4*>(dst + g * 64 + 4) = make_float4(acc_s[4][g], acc_s[5][g], acc_s[6][g], acc_s[7][g]);
+            for (int t = 0; t < 8; ++t)
+#pragma unroll
+                for (int g = 0; g < G; ++g) acc_s[t][g] += __shfl_xor_sync(kFull, acc_s[t][g], 16);
+            if (gi < 2) {
+                float* dst = spart + (static_cast<size_t>(warp * 2 + gi) * G) * 64 + kb * 8;
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    *reinterpret_cast<float4*>(dst + g * 64) = make_float4(acc_s[0][g], acc_s[1][g], acc_s[2][g], acc_s[3][g]);
+                    *reinterpret_cast<float4*>(dst + g * 64 + 4) = make_float4(acc_s[4][g], acc_s[5][g], acc_s[6][g], acc_s[7][g]);
+                }
             }
             __syncthreads();
         }
