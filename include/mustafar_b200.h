@@ -245,6 +245,24 @@ int mfar_decode_attention_quant(
     float softmax_scale, void* out, int64_t out_stride, void* workspace, size_t workspace_bytes, int nsplit,
     uint32_t* dev_status, void* stream);
 
+/* mfar_decode_attention_fp16 for callers that replay a captured launch while the cache grows: the number of
+ * compressed tokens is read from n_tokens_dev (int32 on the device, a multiple of 64) when the kernel runs;
+ * max_tokens (a multiple of 64) bounds it and sizes the grid, the plan (mfar_decode_plan with max_tokens) and
+ * the workspace.  stage_halves must cover the largest 64-token block that will ever be appended
+ * (64 * kept values per token + 7 * 128 of padding is always enough).  Block kernel only: the superblock /
+ * stream flags are refused.  No reference counterpart (the reference re-launches with host-side lengths,
+ * models/llama_mustafar_kernel.py:391-438). */
+int mfar_decode_attention_fp16_dyn(
+    const void* q, int64_t q_stride, int n_kv_heads, int group,
+    const int64_t* k_bitmaps, int64_t k_bmp_head_stride, const int32_t* k_accum, int64_t k_acc_head_stride,
+    const void* k_nz, const int32_t* k_nz_offset, int64_t k_nz_head_stride,
+    const int64_t* v_bitmaps, int64_t v_bmp_head_stride, const int32_t* v_accum, int64_t v_acc_head_stride,
+    const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride,
+    int max_tokens, const int32_t* n_tokens_dev, const void* k_window, const void* v_window, int64_t win_head_stride,
+    int64_t win_token_stride, int window, const int32_t* window_len_dev, float softmax_scale, void* out,
+    int64_t out_stride, void* workspace, size_t workspace_bytes, int nsplit, int stage_halves, int flags,
+    uint32_t* dev_status, void* stream);
+
 /* ---- decode-step glue (no counterpart in the reference's extensions: its model file does these with torch ops) ----
  * Three small fused kernels for the one-token decode step around the sparse attention, so that a layer is a
  * handful of launches.  All tensors fp16, contiguous rows; rounding follows the torch expressions they replace

@@ -35,6 +35,11 @@ SIGNATURES = {
                                           _vp, _i64, _vp, _i64, _vp, _vp, _i64,
                                           _i32, _vp, _vp, _i64, _i64, _i32, _vp, _f32, _vp, _i64, _vp, _sz,
                                           _i32, _i32, _i32, _vp, _vp]),
+    "mfar_decode_attention_fp16_dyn": (_i32, [_vp, _i64, _i32, _i32,
+                                              _vp, _i64, _vp, _i64, _vp, _vp, _i64,
+                                              _vp, _i64, _vp, _i64, _vp, _vp, _i64,
+                                              _i32, _vp, _vp, _vp, _i64, _i64, _i32, _vp, _f32, _vp, _i64, _vp, _sz,
+                                              _i32, _i32, _i32, _vp, _vp]),
     "mfar_key_scores_fp16": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32,
                                     _vp, _i64, _i32, _vp, _vp]),
     "mfar_value_output_fp16": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32,

@@ -115,11 +115,19 @@ __global__ void __launch_bounds__(kThreads, MFAR_MIN_BLOCKS) decode_kernel(Decod
     unsigned sel, mh, ml;
     lane_byte_constants(kb, sel, mh, ml);
 
-    const int blk0 = is_window ? 0 : split * p.bps;
+    // the compressed length may live in device memory too (a captured launch keeps working while blocks are
+    // appended): p.nblk is then its upper bound, the grid was sized for that bound, and the blocks actually there
+    // are dealt out again over the same number of splits (splits past the end write an empty record)
+    int nblk = p.nblk, bps = p.bps;
+    if (p.L_dev) {
+        nblk = max(0, min(*p.L_dev / 64, p.nblk));
+        bps = p.nsplit > 0 ? (nblk + p.nsplit - 1) / p.nsplit : 0;
+    }
+    const int blk0 = is_window ? 0 : split * bps;
     // the window length may live in device memory (so that a captured launch can be replayed while
     // the window grows); p.W is then only its upper bound
     const int W = (is_window && p.W_dev) ? max(0, min(*p.W_dev, p.W)) : p.W;
-    int nb = is_window ? (W + 63) / 64 : min(p.bps, p.nblk - blk0);
+    int nb = is_window ? (W + 63) / 64 : min(bps, nblk - blk0);
     if (nb < 0) nb = 0;
 
     // ---- prologue: q to shared memory, block offsets of this split, barriers
@@ -647,16 +655,19 @@ extern "C" int mfar_decode_plan(int n_kv_heads, int n_tokens, int window, int ns
     return MFAR_OK;
 }
 
-extern "C" int mfar_decode_attention_fp16(
+static int decode_attention_fp16_impl(
     const void* q, int64_t q_stride, int n_kv_heads, int group,
     const int64_t* k_bitmaps, int64_t k_bmp_head_stride, const int32_t* k_accum, int64_t k_acc_head_stride,
     const void* k_nz, const int32_t* k_nz_offset, int64_t k_nz_head_stride,
     const int64_t* v_bitmaps, int64_t v_bmp_head_stride, const int32_t* v_accum, int64_t v_acc_head_stride,
     const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride,
-    int n_tokens, const void* k_window, const void* v_window, int64_t win_head_stride, int64_t win_token_stride,
-    int window, const int32_t* window_len_dev, float softmax_scale, void* out, int64_t out_stride, void* workspace,
-    size_t workspace_bytes, int nsplit, int stage_halves, int flags, uint32_t* dev_status, void* stream) {
+    int n_tokens, const int32_t* n_tokens_dev, const void* k_window, const void* v_window, int64_t win_head_stride,
+    int64_t win_token_stride, int window, const int32_t* window_len_dev, float softmax_scale, void* out,
+    int64_t out_stride, void* workspace, size_t workspace_bytes, int nsplit, int stage_halves, int flags,
+    uint32_t* dev_status, void* stream) {
     if (n_kv_heads <= 0 || group <= 0 || n_tokens < 0 || (n_tokens % 64) || window < 0) return MFAR_ERR_ARG;
+    // a device-resident length is a feature of the block kernel only
+    if (n_tokens_dev && (flags & (MFAR_DECODE_FORCE_SUPERBLOCK | MFAR_DECODE_FORCE_STREAM))) return MFAR_ERR_ARG;
     if (n_tokens == 0 && window == 0) return MFAR_ERR_ARG;
     if (group != 1 && group != 2 && group != 4 && group != 8) return MFAR_ERR_ARG;
     if (!q || !out || !workspace) return MFAR_ERR_ARG;
@@ -689,6 +700,7 @@ extern "C" int mfar_decode_attention_fp16(
     p.win_ts = win_token_stride;
     p.W = window;
     p.W_dev = window_len_dev;
+    p.L_dev = n_tokens_dev;
     p.nblk = n_tokens / 64;
     p.cap = pick_cap(stage_halves);
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
@@ -745,6 +757,42 @@ extern "C" int mfar_decode_attention_fp16(
     }
     combine_kernel<<<n_kv_heads * group, 128, 0, s>>>(p.ws, nrec, group, 1, static_cast<__half*>(out), out_stride);
     return launch_status();
+}
+
+extern "C" int mfar_decode_attention_fp16(
+    const void* q, int64_t q_stride, int n_kv_heads, int group,
+    const int64_t* k_bitmaps, int64_t k_bmp_head_stride, const int32_t* k_accum, int64_t k_acc_head_stride,
+    const void* k_nz, const int32_t* k_nz_offset, int64_t k_nz_head_stride,
+    const int64_t* v_bitmaps, int64_t v_bmp_head_stride, const int32_t* v_accum, int64_t v_acc_head_stride,
+    const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride,
+    int n_tokens, const void* k_window, const void* v_window, int64_t win_head_stride, int64_t win_token_stride,
+    int window, const int32_t* window_len_dev, float softmax_scale, void* out, int64_t out_stride, void* workspace,
+    size_t workspace_bytes, int nsplit, int stage_halves, int flags, uint32_t* dev_status, void* stream) {
+    return decode_attention_fp16_impl(q, q_stride, n_kv_heads, group, k_bitmaps, k_bmp_head_stride, k_accum,
+                                      k_acc_head_stride, k_nz, k_nz_offset, k_nz_head_stride, v_bitmaps, v_bmp_head_stride,
+                                      v_accum, v_acc_head_stride, v_nz, v_nz_offset, v_nz_head_stride, n_tokens, nullptr,
+                                      k_window, v_window, win_head_stride, win_token_stride, window, window_len_dev,
+                                      softmax_scale, out, out_stride, workspace, workspace_bytes, nsplit, stage_halves,
+                                      flags, dev_status, stream);
+}
+
+extern "C" int mfar_decode_attention_fp16_dyn(
+    const void* q, int64_t q_stride, int n_kv_heads, int group,
+    const int64_t* k_bitmaps, int64_t k_bmp_head_stride, const int32_t* k_accum, int64_t k_acc_head_stride,
+    const void* k_nz, const int32_t* k_nz_offset, int64_t k_nz_head_stride,
+    const int64_t* v_bitmaps, int64_t v_bmp_head_stride, const int32_t* v_accum, int64_t v_acc_head_stride,
+    const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride,
+    int max_tokens, const int32_t* n_tokens_dev, const void* k_window, const void* v_window, int64_t win_head_stride,
+    int64_t win_token_stride, int window, const int32_t* window_len_dev, float softmax_scale, void* out,
+    int64_t out_stride, void* workspace, size_t workspace_bytes, int nsplit, int stage_halves, int flags,
+    uint32_t* dev_status, void* stream) {
+    if (!n_tokens_dev) return MFAR_ERR_ARG;
+    return decode_attention_fp16_impl(q, q_stride, n_kv_heads, group, k_bitmaps, k_bmp_head_stride, k_accum,
+                                      k_acc_head_stride, k_nz, k_nz_offset, k_nz_head_stride, v_bitmaps, v_bmp_head_stride,
+                                      v_accum, v_acc_head_stride, v_nz, v_nz_offset, v_nz_head_stride, max_tokens,
+                                      n_tokens_dev, k_window, v_window, win_head_stride, win_token_stride, window,
+                                      window_len_dev, softmax_scale, out, out_stride, workspace, workspace_bytes, nsplit,
+                                      stage_halves, flags, dev_status, stream);
 }
 
 extern "C" int mfar_key_scores_fp16(const void* q, int64_t q_stride, int n_kv_heads, int group,

@@ -196,6 +196,7 @@ struct DecodeParams {
     int64_t win_hs, win_ts;
     int W;
     const int* W_dev;      // optional: window length in device memory (then W is its upper bound)
+    const int* L_dev;      // optional: compressed tokens in device memory (then nblk is their upper bound, in blocks)
     int nblk, nsplit, bps; // compressed blocks, splits over them, blocks per split
     int cap;               // halves of packed values a stage can hold per tensor
     float scale_log2;      // softmax scale * log2(e)

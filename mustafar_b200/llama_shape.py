@@ -125,6 +125,10 @@ class SparseLlama:
         self._eager_done = False
         self._inv_freq = None
         self._qbuf = None
+        # largest packed size of a 64-token block that can still come (what a replayed launch stages for): the kept
+        # values of 64 tokens, a few ties, and the worst padding of its 128 tiles
+        kept = D - self.rank_keep + 1
+        self._stage_bound = min(8192, 64 * (kept + 3) + 7 * 128)
 
     # ------------------------------------------------------------------ pieces
     def _allreduce(self, x):
@@ -222,7 +226,7 @@ class SparseLlama:
         if self._inv_freq is None:
             self._inv_freq = step_ops.rope_inv_freq(self.s.rope_theta, self.dev)
             self._qbuf = torch.empty(B * self.hq, D, dtype=torch.float16, device=self.dev)
-        hint = self._hint()
+        hint = 0 if dev_state else self._hint()
         w = self.wlen
         tp = self.tp_world > 1
         x = self.embed[token]                     # [B, hidden], updated in place from here on
@@ -233,8 +237,8 @@ class SparseLlama:
             if dev_state:
                 step_ops.rope_append(qkv, self._inv_freq, self._state[0:1], self._state[1:2], self.hq, self.hkv,
                                      self._qbuf, L.kwin, L.vwin)
-                att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin, L.vwin, self.G, stage_halves=hint,
-                                           window_len=self._state[2:3])
+                att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin, L.vwin, self.G, stage_halves=self._stage_bound,
+                                           window_len=self._state[2:3], n_tokens=self._state[3:4])
             else:
                 step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin)
                 att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G,
@@ -247,7 +251,7 @@ class SparseLlama:
             if tp:
                 yield delta
         if dev_state:
-            self._state += 1
+            self._state += self._state_step
         self._step_out = F.linear(step_ops.add_rmsnorm(x, delta, self.norm, eps), self.lm_head)
 
     def _step_body_fused(self, token: torch.Tensor, dev_state: bool) -> torch.Tensor:
@@ -288,15 +292,23 @@ class SparseLlama:
         self.wlen += 1
         if self.wlen == self.wcap:
             self._compress_oldest()
-            self._graph = None
+            if self._graph is not None:
+                # the captured launches read their lengths on the device: move the window back by one block and
+                # the compressed length forward; nothing is re-captured
+                self._state += self._state_append
+                for L in self.layers:
+                    L.ks.check()
+                    L.vs.check()
+                ops.check_device_status()       # e.g. a block larger than the replayed launches stage for
 
     @torch.no_grad()
     def decode_step(self, token: torch.Tensor, graph: bool = False) -> torch.Tensor:
         """token [B] (ids of the newest position) -> logits [B, vocab].
 
-        graph=True replays CUDA graphs of the step (re-captured after every 256-token block append, because
-        the compressed length is a launch argument); the first step of each epoch runs eagerly.  Under tensor
-        parallelism the step is a chain of graphs with the NCCL all-reduces launched between them."""
+        graph=True replays CUDA graphs of the step, captured once after a first eager step: position, window
+        length and compressed length live in a device tensor that the captured kernels read, so appending a block
+        needs no new capture.  Under tensor parallelism the step is a chain of graphs with the NCCL all-reduces
+        launched between them."""
         if not (graph and self.sparse):
             out = self._step_body(token, False)
             self._advance()
@@ -307,10 +319,12 @@ class SparseLlama:
                 out = self._step_body(token, False)       # sizes workspaces, resolves the stage hint
                 self._advance()
                 return out
-            # position, window slot of the new token, window length: read on the device by the captured kernels
-            self._state = torch.tensor([self.tokens, self.wlen, self.wlen + 1], device=self.dev, dtype=torch.int32)
+            # position, window slot of the new token, window length, compressed length: read on the device
+            self._state = torch.tensor([self.tokens, self.wlen, self.wlen + 1, self.compressed], device=self.dev,
+                                       dtype=torch.int32)
+            self._state_step = torch.tensor([1, 1, 1, 0], device=self.dev, dtype=torch.int32)
+            self._state_append = torch.tensor([0, -256, -256, 256], device=self.dev, dtype=torch.int32)
             self._tok_buf = token.clone()
-            self._hint()
             torch.cuda.synchronize()
             self._graph = self._capture_step()
         self._tok_buf.copy_(token)
@@ -319,7 +333,6 @@ class SparseLlama:
             if partial is not None:
                 self.dist.all_reduce(partial)
         out = self._step_out
-        self._eager_done = False if self.wlen + 1 == self.wcap else self._eager_done
         self._advance()
         return out
 

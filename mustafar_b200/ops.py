@@ -139,7 +139,7 @@ def decode_attention(q: torch.Tensor, k_store: SparseStore, v_store: SparseStore
                      k_window: torch.Tensor | None, v_window: torch.Tensor | None,
                      group: int, softmax_scale: float | None = None, out: torch.Tensor | None = None,
                      nsplit: int = 0, stage_halves: int | None = None, variant: str = "auto",
-                     window_len: torch.Tensor | None = None) -> torch.Tensor:
+                     window_len: torch.Tensor | None = None, n_tokens: torch.Tensor | None = None) -> torch.Tensor:
     """Fused decode attention of one query token per q-head.
 
     q [n_kv_heads*group, 128] fp16; k_store / v_store hold the compressed tokens;
@@ -148,6 +148,10 @@ def decode_attention(q: torch.Tensor, k_store: SparseStore, v_store: SparseStore
     "superblock", "stream" or "stream16" (stream kernel with fp16 coefficients) pins the kernel.
     ``window_len``: optional CUDA int32 tensor [1] with the number of valid window tokens (the window
     tensors then give the capacity); a captured launch can so be replayed while the window grows.
+    ``n_tokens``: optional CUDA int32 tensor [1] with the number of compressed tokens to attend to (a multiple
+    of 64, at most ``k_store.max_tokens``): the launch is then sized for the stores' capacity and keeps working
+    while blocks are appended.  ``stage_halves`` must then cover every block still to come
+    (``64 * kept + 896`` always does).  Block kernel only.
     Returns fp16 [n_kv_heads*group, 128].
     """
     n_kv = k_store.n_heads
@@ -172,19 +176,41 @@ def decode_attention(q: torch.Tensor, k_store: SparseStore, v_store: SparseStore
         softmax_scale = 1.0 / math.sqrt(D)
     if out is None:
         out = torch.empty((n_kv * group, D), dtype=torch.float16, device=q.device)
-    if stage_halves is None:
+    if stage_halves is None and n_tokens is None:
         stage_halves = max(k_store.stage_hint(), v_store.stage_hint()) if L else 8
+    flags = {"auto": 0, "block": 1, "block32": 17, "superblock": 2, "stream": 4, "stream16": 12}[variant]
+    wl = None if window_len is None else window_len.data_ptr()
+    st = _dev_status(q.device)
+    if n_tokens is not None:
+        if not n_tokens.is_cuda or n_tokens.dtype != torch.int32 or n_tokens.numel() != 1:
+            raise RuntimeError("n_tokens must be a CUDA int32 tensor with one element")
+        if stage_halves is None:
+            raise RuntimeError("n_tokens on the device needs an explicit stage_halves bound")
+        Lmax = min(k_store.max_tokens, v_store.max_tokens)
+        _, nbytes = plan(n_kv, Lmax, W, group, nsplit)
+        ws = _workspace(q.device, nbytes)
+        r = _lib.lib().mfar_decode_attention_fp16_dyn(
+            q.data_ptr(), q.stride(0), n_kv, group,
+            k_store.bitmaps.data_ptr(), k_store.tiles_cap, k_store.accum.data_ptr(), k_store.tiles_cap + 1,
+            k_store.nz.data_ptr(), None, k_store.nz_capacity,
+            v_store.bitmaps.data_ptr(), v_store.tiles_cap, v_store.accum.data_ptr(), v_store.tiles_cap + 1,
+            v_store.nz.data_ptr(), None, v_store.nz_capacity,
+            Lmax, n_tokens.data_ptr(), kw, vw, wh, wt, W, wl, float(softmax_scale), out.data_ptr(), out.stride(0),
+            ws.data_ptr(), ws.numel(), nsplit, stage_halves, flags, st.data_ptr(), _stream())
+        _lib.check(r, "mfar_decode_attention_fp16_dyn")
+        if _debug_check():
+            check_device_status(q.device)
+        return out
     _, nbytes = plan(n_kv, L, W, group, nsplit)
     ws = _workspace(q.device, nbytes)
-    st = _dev_status(q.device)
     r = _lib.lib().mfar_decode_attention_fp16(
         q.data_ptr(), q.stride(0), n_kv, group,
         k_store.bitmaps.data_ptr(), k_store.tiles_cap, k_store.accum.data_ptr(), k_store.tiles_cap + 1,
         k_store.nz.data_ptr(), None, k_store.nz_capacity,
         v_store.bitmaps.data_ptr(), v_store.tiles_cap, v_store.accum.data_ptr(), v_store.tiles_cap + 1,
         v_store.nz.data_ptr(), None, v_store.nz_capacity,
-        L, kw, vw, wh, wt, W, None if window_len is None else window_len.data_ptr(), float(softmax_scale), out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(),
-        nsplit, stage_halves, {"auto": 0, "block": 1, "block32": 17, "superblock": 2, "stream": 4, "stream16": 12}[variant], st.data_ptr(), _stream())
+        L, kw, vw, wh, wt, W, wl, float(softmax_scale), out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(),
+        nsplit, stage_halves, flags, st.data_ptr(), _stream())
     _lib.check(r, "mfar_decode_attention_fp16")
     if _debug_check():
         check_device_status(q.device)

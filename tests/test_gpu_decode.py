@@ -144,3 +144,38 @@ def test_op_argument_errors(m):
         m.o.mustafar_key_formulation(bmp.int(), nz, idx, off, q, 64, 128, 1, 1)
     with pytest.raises(RuntimeError):
         m.o.mustafar_key_formulation(bmp.cpu(), nz, idx, off, q, 64, 128, 1, 1)
+
+
+@pytest.mark.parametrize("L", [0, 64, 512, 1024])
+def test_device_resident_length_matches_host_length(L):
+    """mfar_decode_attention_fp16_dyn: the launch is sized for the stores' capacity (1024 tokens), the number of
+    compressed tokens is read on the device; the result equals the host-length call for the same cache state."""
+    from mustafar_b200 import compression as comp, ops
+    Bh, G, cap_tokens, W = 4, 4, 1024, 96
+    k, v = oracle.make_kv(Bh, cap_tokens, seed=321)
+    kw, vw = oracle.make_kv(Bh, W, seed=322)
+    q = oracle.make_query(Bh * G, seed=9).cuda()
+    rank = comp.keep_rank(0.7)
+    ks, vs = comp.SparseStore(Bh, cap_tokens, comp.KEY, "cuda"), comp.SparseStore(Bh, cap_tokens, comp.VALUE, "cuda")
+    if L:
+        ks.append(k[:, :L].cuda(), rank)
+        vs.append(v[:, :L].cuda(), rank)
+    want = ops.decode_attention(q, ks, vs, kw.cuda(), vw.cuda(), G)
+    n_dev = torch.tensor([L], dtype=torch.int32, device="cuda")
+    got = ops.decode_attention(q, ks, vs, kw.cuda(), vw.cuda(), G, n_tokens=n_dev, stage_halves=64 * rank_keep(0.7) + 896)
+    ops.check_device_status()
+    assert oracle.rel_l2(got.float().cpu(), want.float().cpu()) < 1e-3
+    # appending one more block and bumping the device counter is all a replayed launch needs
+    if L + 64 <= cap_tokens:
+        ks.append(k[:, L:L + 64].cuda(), rank)
+        vs.append(v[:, L:L + 64].cuda(), rank)
+        n_dev += 64
+        want2 = ops.decode_attention(q, ks, vs, kw.cuda(), vw.cuda(), G)
+        got2 = ops.decode_attention(q, ks, vs, kw.cuda(), vw.cuda(), G, n_tokens=n_dev, stage_halves=64 * rank_keep(0.7) + 896)
+        assert oracle.rel_l2(got2.float().cpu(), want2.float().cpu()) < 1e-3
+
+
+def rank_keep(sparsity):
+    """values kept per token (of 128) at this sparsity: 128 - keep_rank + 1"""
+    from mustafar_b200 import compression as comp
+    return 128 - comp.keep_rank(sparsity) + 1
