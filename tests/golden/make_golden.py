@@ -168,7 +168,7 @@ def cases(prune):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (Haozon/mustafar)")
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     comp = _load(os.path.join(a.reference, "kernel", "compression.py"), "ref_compression")
