@@ -74,7 +74,7 @@ __device__ __forceinline__ float warp_sum_f32(float v) {
 // (K phase: the query channel; V phase: the probability of the token).  The compiler turns
 // the `if` into predicated instructions (no branch, no zero fill).
 #ifndef MFAR_CHAINS
-#define MFAR_CHAINS 1
+#define MFAR_CHAINS 2
 #endif
 template <int G>
 __device__ __forceinline__ void tile_step(unsigned hi, unsigned lo, const unsigned short* vals, unsigned sel,
@@ -132,6 +132,24 @@ template <int G>
 __device__ __forceinline__ void tile_step(unsigned hi, unsigned lo, const unsigned short* vals, unsigned sel,
                                           unsigned mh, unsigned ml, const unsigned short (&coef)[G], float (&acc)[8][G]) {
     const unsigned byte = __byte_perm(lo, hi, sel);
+#if MFAR_CHAINS >= 2
+    // MFAR_CHAINS read pointers (8 / MFAR_CHAINS positions each) shorten the dependent chain of pointer bumps
+    const unsigned short* pv[MFAR_CHAINS];
+    pv[0] = vals + (__popc(hi & mh) + __popc(lo & ml));
+#pragma unroll
+    for (int c = 1; c < MFAR_CHAINS; ++c)
+        pv[c] = pv[0] + __popc(byte & (0xffu & ~(0xffu >> (c * (8 / MFAR_CHAINS)))));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (byte & (0x80u >> i)) {
+            const unsigned short*& p = pv[i / (8 / MFAR_CHAINS)];
+            const unsigned short v = *p;
+            ++p;
+#pragma unroll
+            for (int g = 0; g < G; ++g) acc[i][g] = fma_h(acc[i][g], v, coef[g]);
+        }
+    }
+#else
     const unsigned short* pv = vals + (__popc(hi & mh) + __popc(lo & ml));
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -142,6 +160,7 @@ __device__ __forceinline__ void tile_step(unsigned hi, unsigned lo, const unsign
             for (int g = 0; g < G; ++g) acc[i][g] = fma_h(acc[i][g], v, coef[g]);
         }
     }
+#endif
 }
 
 template <int G>
