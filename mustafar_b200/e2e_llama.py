@@ -31,6 +31,8 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--no-graph", action="store_true", help="launch every decode step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--dense", action="store_true", help="dense pruned cache + torch attention (comparison arm)")
+    ap.add_argument("--bits", type=int, default=16, choices=[16, 4, 2],
+                    help="16: pruned values kept as fp16; 4 / 2: quantised per tile (decode steps run eagerly)")
     a = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -43,7 +45,7 @@ def main():
     tp = world if a.parallel == "tp" else 1
     shape = LlamaShape(n_layers=a.layers)
     model = SparseLlama(shape, a.batch, a.prompt + a.new, dev, sparsity=a.sparsity, seed=1234,
-                        tp_rank=rank if tp > 1 else 0, tp_world=tp, dist=dist, sparse=not a.dense)
+                        tp_rank=rank if tp > 1 else 0, tp_world=tp, dist=dist, sparse=not a.dense, cache_bits=a.bits)
     g = torch.Generator(device=dev).manual_seed(99 if tp > 1 else 99 + rank)
     toks = torch.randint(0, shape.vocab, (a.batch, a.prompt), generator=g, device=dev)
 
@@ -72,15 +74,28 @@ def main():
     prefill_ms = max_over_ranks(e[0].elapsed_time(e[1]), dist, dev)
     decode_ms = max_over_ranks(e[1].elapsed_time(e[2]), dist, dev)
     seqs = a.batch * (1 if tp > 1 else world)
+    # bytes the compressed part of the cache takes per (token, kv head), K + V, measured on the first layer of this rank
+    cache_bytes = None
+    if not a.dense and model.compressed:
+        L0 = model.layers[0]
+        per = 0.0
+        for st in (L0.ks, L0.vs):
+            tiles = 2 * model.compressed
+            if a.bits == 16:
+                per += 8 * tiles + 4 * (tiles + 1) + 2.0 * float(st.packed_lengths().float().mean())
+            else:
+                per += (8 + 4 + 2 + 2) * tiles + 4.0 * float(st.head_tail.float().mean())
+        cache_bytes = per / model.compressed
     if rank == 0:
         print(json.dumps({
             "metric": "llama3_8b_shape_decode_throughput", "unit": "tok/s", "n_gpus": world,
             "value": seqs * (a.new - 1) / (decode_ms * 1e-3), "tpot_ms": decode_ms / (a.new - 1), "tpot_median_ms": steady_ms,
             "slowest_step_ms": slowest_ms, "ttft_ms": prefill_ms,
+            "compressed_cache_bytes_per_token_per_kv_head": cache_bytes, "dense_fp16_bytes_per_token_per_kv_head": 512,
             "config": {"workload": f"Llama-3-8B shape, {a.layers} layers, prompt {a.prompt}, {a.new} new tokens, "
                                    f"batch {a.batch} per {'job' if tp > 1 else 'GPU'}, sparsity {a.sparsity}, window 128",
-                       "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}", "cache": "dense-pruned torch" if a.dense else "sparse fp16",
-                       "cuda_graph": (False if (a.no_graph or a.dense) else ("one graph per stretch between collectives" if tp > 1 else True))},
+                       "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}", "cache": "dense-pruned torch" if a.dense else ("sparse fp16" if a.bits == 16 else f"sparse {a.bits}-bit"),
+                       "cuda_graph": (False if (a.no_graph or a.dense or a.bits != 16) else ("one graph per stretch between collectives" if tp > 1 else True))},
             "data": "synthetic (random-init weights, random prompt ids)", "dtype": "f16"}))
     if dist is not None:
         dist.barrier()

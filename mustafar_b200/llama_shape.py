@@ -25,7 +25,8 @@ import torch
 import torch.nn.functional as F
 
 from . import compression as comp
-from . import ops, step_ops
+from . import compression_quant as cq
+from . import ops, ops_quant, step_ops
 
 D = 128
 
@@ -71,10 +72,14 @@ class SparseLlama:
 
     def __init__(self, shape: LlamaShape, batch: int, max_tokens: int, device, sparsity: float = 0.7,
                  residual: int = 128, seed: int = 0, tp_rank: int = 0, tp_world: int = 1, dist=None,
-                 sparse: bool = True):
+                 sparse: bool = True, cache_bits: int = 16):
         assert shape.n_kv_heads % tp_world == 0 and shape.ffn % tp_world == 0
         self.s, self.B, self.dev = shape, batch, torch.device(device)
         self.sparsity, self.residual, self.sparse = sparsity, residual, sparse
+        # 16: pruned values kept as fp16; 2 or 4: pruned values quantised per tile (the reference's quantised model,
+        # models/llama_mustafar_quant_kernel.py); the quantised cache runs its decode steps eagerly
+        assert cache_bits in (16, 2, 4)
+        self.cache_bits, self.quant = cache_bits, sparse and cache_bits != 16
         self.tp_rank, self.tp_world, self.dist = tp_rank, tp_world, dist
         self.hq = shape.n_q_heads // tp_world
         self.hkv = shape.n_kv_heads // tp_world
@@ -110,9 +115,14 @@ class SparseLlama:
             L.n2 = torch.ones(hd, dtype=torch.float16, device=self.dev)
             del wq, wk, wv, wg, wu
             if sparse:
-                cap = int(self.max_tokens * D * min(1.0, (1.0 - sparsity) + 0.25)) // 8 * 8
-                L.ks = comp.SparseStore(Bh, self.max_tokens, comp.KEY, self.dev, nz_capacity=cap)
-                L.vs = comp.SparseStore(Bh, self.max_tokens, comp.VALUE, self.dev, nz_capacity=cap)
+                if self.quant:
+                    # code arena sized for the worst case (every tile full): 64 * bits / 32 words per tile
+                    L.ks = cq.QuantStore(Bh, self.max_tokens, comp.KEY, self.dev, cache_bits, 64)
+                    L.vs = cq.QuantStore(Bh, self.max_tokens, comp.VALUE, self.dev, cache_bits, 64)
+                else:
+                    cap = int(self.max_tokens * D * min(1.0, (1.0 - sparsity) + 0.25)) // 8 * 8
+                    L.ks = comp.SparseStore(Bh, self.max_tokens, comp.KEY, self.dev, nz_capacity=cap)
+                    L.vs = comp.SparseStore(Bh, self.max_tokens, comp.VALUE, self.dev, nz_capacity=cap)
                 L.kwin = torch.empty(Bh, self.wcap, D, dtype=torch.float16, device=self.dev)
                 L.vwin = torch.empty(Bh, self.wcap, D, dtype=torch.float16, device=self.dev)
             else:   # dense reference cache: pruned tokens kept with their zeros (the torch accuracy path)
@@ -226,7 +236,7 @@ class SparseLlama:
         if self._inv_freq is None:
             self._inv_freq = step_ops.rope_inv_freq(self.s.rope_theta, self.dev)
             self._qbuf = torch.empty(B * self.hq, D, dtype=torch.float16, device=self.dev)
-        hint = 0 if dev_state else self._hint()
+        hint = 0 if (dev_state or self.quant) else self._hint()
         w = self.wlen
         tp = self.tp_world > 1
         x = self.embed[token]                     # [B, hidden], updated in place from here on
@@ -239,6 +249,10 @@ class SparseLlama:
                                      self._qbuf, L.kwin, L.vwin)
                 att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin, L.vwin, self.G, stage_halves=self._stage_bound,
                                            window_len=self._state[2:3], n_tokens=self._state[3:4])
+            elif self.quant:
+                step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin)
+                att = ops_quant.decode_attention_quant(self._qbuf, L.ks.as_dict(), L.vs.as_dict(), self.compressed,
+                                                       L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G, self.cache_bits)
             else:
                 step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin)
                 att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G,
@@ -309,7 +323,7 @@ class SparseLlama:
         length and compressed length live in a device tensor that the captured kernels read, so appending a block
         needs no new capture.  Under tensor parallelism the step is a chain of graphs with the NCCL all-reduces
         launched between them."""
-        if not (graph and self.sparse):
+        if not (graph and self.sparse and not self.quant):
             out = self._step_body(token, False)
             self._advance()
             return out

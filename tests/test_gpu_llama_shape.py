@@ -55,3 +55,28 @@ def test_generate_runs_and_is_deterministic():
     a = SparseLlama(shape, 1, 512, "cuda", seed=9).generate(toks, 8)
     b = SparseLlama(shape, 1, 512, "cuda", seed=9).generate(toks, 8)
     assert a.shape == (1, 8) and torch.equal(a, b)
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+def test_quantised_cache_model_matches_dense_model_with_dequantised_cache(bits):
+    """The quantised cache end to end: after the prefill the dense comparison model gets its compressed tokens
+    replaced by what the oracle's quantise -> dequantise gives for them; the decode steps of both models then agree."""
+    from mustafar_b200.llama_shape import SparseLlama, tiny_shape
+    shape, B, prompt = tiny_shape(), 2, 256 + 128 + 40
+    toks = torch.randint(0, shape.vocab, (B, prompt), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+    qm = SparseLlama(shape, B, 1024, "cuda", seed=3, cache_bits=bits)
+    dm = SparseLlama(shape, B, 1024, "cuda", seed=3, sparse=False)
+    lq, ld = qm.prefill(toks), dm.prefill(toks)
+    assert qm.compressed == 256 == dm.compressed
+    for L in dm.layers:
+        k = L.ks[:, :256].cpu()
+        v = L.vs[:, :256].cpu()
+        kf = oracle.quant_format.quant_compress_key_ref(k, bits, 64)
+        vf = oracle.quant_format.quant_compress_value_ref(v, bits, 64)
+        L.ks[:, :256] = torch.as_tensor(oracle.quant_format.dequant_key_ref(kf, 256, 128, bits, 64)).cuda()
+        L.vs[:, :256] = torch.as_tensor(oracle.quant_format.dequant_value_ref(vf, 256, 128, bits, 64)).cuda()
+    nxt = ld.argmax(-1)
+    for i in range(6):
+        lq, ld = qm.decode_step(nxt, graph=True), dm.decode_step(nxt)   # graph=True falls back to eager for this cache
+        assert oracle.rel_l2(lq.float().cpu(), ld.float().cpu()) < 5e-3, i
+        nxt = ld.argmax(-1)
