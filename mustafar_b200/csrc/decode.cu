@@ -108,7 +108,9 @@ __global__ void __launch_bounds__(kThreads, MFAR_MIN_BLOCKS) decode_kernel(Decod
     int* vblk = reinterpret_cast<int*>(smem + lay.vblk);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int h = blockIdx.y;
+    // hq numbers the (kv head, group of G query heads) pairs; with kv_share > 1 several of them read the same kv head
+    const int hq = blockIdx.y;
+    const int h = hq / (p.kv_share > 0 ? p.kv_share : 1);
     const int split = blockIdx.x + p.split_offset;
     const bool is_window = (MODE == MODE_ATTN) && (split == p.nsplit);
     const int gi = lane >> 3, kb = lane & 7;
@@ -134,7 +136,7 @@ __global__ void __launch_bounds__(kThreads, MFAR_MIN_BLOCKS) decode_kernel(Decod
     if (MODE != MODE_VALUE) {
         for (int i = tid; i < kD * G; i += kThreads) {
             const int c = i / G, g = i % G;
-            store_coef(&qs[i], __half2float(p.q[(static_cast<int64_t>(h) * G + g) * p.q_stride + c]));
+            store_coef(&qs[i], __half2float(p.q[(static_cast<int64_t>(hq) * G + g) * p.q_stride + c]));
         }
     }
     const int* kacc = p.k.acc + h * p.k.acc_hs;
@@ -327,7 +329,7 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
             // p comes from the caller: warp j loads heads j, j+4, ...; lane takes tokens 2*lane, 2*lane+1
             for (int g = warp; g < G; g += kWarps) {
                 const __half2 pv = *reinterpret_cast<const __half2*>(
-                    p.p_in + (static_cast<int64_t>(h) * G + g) * p.p_stride + static_cast<int64_t>(blk0 + i) * 64 + 2 * lane);
+                    p.p_in + (static_cast<int64_t>(hq) * G + g) * p.p_stride + static_cast<int64_t>(blk0 + i) * 64 + 2 * lane);
                 store_coef(&ps[(2 * lane) * G + g], __low2float(pv));
                 store_coef(&ps[(2 * lane + 1) * G + g], __high2float(pv));
             }
@@ -348,7 +350,7 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
                         s1 += t.y;
                     }
                     if (MODE == MODE_KEY) {
-                        *reinterpret_cast<__half2*>(p.s_out + (static_cast<int64_t>(h) * G + g) * p.s_stride +
+                        *reinterpret_cast<__half2*>(p.s_out + (static_cast<int64_t>(hq) * G + g) * p.s_stride +
                                                     static_cast<int64_t>(blk0 + i) * 64 + 2 * lane) = __floats2half2_rn(s0, s1);
                     } else {
                         s0 *= p.scale_log2;
@@ -456,7 +458,7 @@ MFAR_UNROLL(MFAR_STEP_UNROLL)
     }
     __syncthreads();
     const int nrec = (MODE == MODE_ATTN) ? p.nsplit + (p.W > 0 ? 1 : 0) : p.nsplit;
-    float* rec = p.ws + ((static_cast<int64_t>(h) * nrec + split) * G) * kPartialStride;
+    float* rec = p.ws + ((static_cast<int64_t>(hq) * nrec + split) * G) * kPartialStride;
     for (int idx = tid; idx < G * kD; idx += kThreads) {
         const int g = idx / kD, c = idx % kD;
         float s = 0.f;
@@ -554,7 +556,8 @@ static int launch_decode(const DecodeParams& p, int n_kv_heads, int grid_x, cuda
 // fp32_coef: keep q / the probabilities in fp32 (ATTN only; KEY and VALUE take fp16 coefficients as
 // inputs, so the fp16 path is exact for them and always used)
 template <int MODE>
-static int dispatch_decode(const DecodeParams& p, int G, int n_kv_heads, int grid_x, cudaStream_t s, bool fp32_coef = false) {
+static int dispatch_decode(const DecodeParams& p, int G, int n_kv_heads, int grid_x, cudaStream_t s, bool fp32_coef = false,
+                           bool split8 = true) {
 #define MFAR_BLK(GG)                                                                      \
     case GG:                                                                              \
         if (MODE == MODE_ATTN && fp32_coef) return launch_decode<GG, MODE, false>(p, n_kv_heads, grid_x, s); \
@@ -563,7 +566,19 @@ static int dispatch_decode(const DecodeParams& p, int G, int n_kv_heads, int gri
         MFAR_BLK(1)
         MFAR_BLK(2)
         MFAR_BLK(4)
-        MFAR_BLK(8)
+        case 8: {
+            if (!split8) {   // records in the [kv head][record][8] layout that the stream / superblock kernels write
+                if (MODE == MODE_ATTN && fp32_coef) return launch_decode<8, MODE, false>(p, n_kv_heads, grid_x, s);
+                return launch_decode<8, MODE, true>(p, n_kv_heads, grid_x, s);
+            }
+            // 8 query heads per kv head need 64 accumulators per phase and spill badly (measured 8x the time of
+            // group 4); two CTAs of 4 query heads each read the same kv head instead (the second read hits L2); their partial
+            // records lie in the [kv head * 2 + half][record][4] layout, which the combine kernel reads with G = 4
+            DecodeParams p2 = p;
+            p2.kv_share = 2 * (p.kv_share > 0 ? p.kv_share : 1);
+            if (MODE == MODE_ATTN && fp32_coef) return launch_decode<4, MODE, false>(p2, 2 * n_kv_heads, grid_x, s);
+            return launch_decode<4, MODE, true>(p2, 2 * n_kv_heads, grid_x, s);
+        }
         default: return MFAR_ERR_ARG;
     }
 #undef MFAR_BLK
@@ -610,7 +625,7 @@ int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G,
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.ws = ws;
     p.dev_status = dev_status;
-    return dispatch_decode<MODE_ATTN>(p, G, n_kv_heads, 1, s);
+    return dispatch_decode<MODE_ATTN>(p, G, n_kv_heads, 1, s, false, false);
 }
 
 }  // namespace mfar
@@ -719,6 +734,7 @@ static int decode_attention_fp16_impl(
 
     const bool use_stream = (flags & MFAR_DECODE_FORCE_STREAM) && p.nblk > 0;
     int nrec;
+    int combine_group = group;
     if (use_stream) {
         const int mb = decode_stream_max_blocks();
         if (ns * mb < p.nblk) ns = (p.nblk + mb - 1) / mb;
@@ -745,7 +761,7 @@ static int decode_attention_fp16_impl(
             DecodeParams pw = p;
             pw.split_offset = ns;
             pw.cap = 8;
-            r = dispatch_decode<MODE_ATTN>(pw, group, n_kv_heads, 1, s);
+            r = dispatch_decode<MODE_ATTN>(pw, group, n_kv_heads, 1, s, false, false);
             if (r) return r;
         }
     } else {
@@ -754,8 +770,9 @@ static int decode_attention_fp16_impl(
         nrec = ns + (window > 0 ? 1 : 0);
         r = dispatch_decode<MODE_ATTN>(p, group, n_kv_heads, nrec, s, (flags & MFAR_DECODE_FP32_COEF) != 0);
         if (r) return r;
+        if (group == 8) combine_group = 4;   // the block kernel ran as two groups of 4 per kv head
     }
-    combine_kernel<<<n_kv_heads * group, 128, 0, s>>>(p.ws, nrec, group, 1, static_cast<__half*>(out), out_stride);
+    combine_kernel<<<n_kv_heads * group, 128, 0, s>>>(p.ws, nrec, combine_group, 1, static_cast<__half*>(out), out_stride);
     return launch_status();
 }
 
@@ -856,7 +873,8 @@ extern "C" int mfar_value_output_fp16(const void* probs, int64_t probs_stride, i
     p.dev_status = dev_status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     r = dispatch_decode<MODE_VALUE>(p, group, n_kv_heads, ns, s);
+    const int combine_group = group == 8 ? 4 : group;
     if (r) return r;
-    combine_kernel<<<n_kv_heads * group, 128, 0, s>>>(p.ws, ns, group, 0, static_cast<__half*>(out), out_stride);
+    combine_kernel<<<n_kv_heads * group, 128, 0, s>>>(p.ws, ns, combine_group, 0, static_cast<__half*>(out), out_stride);
     return launch_status();
 }

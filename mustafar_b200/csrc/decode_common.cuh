@@ -216,6 +216,7 @@ struct DecodeParams {
     int W;
     const int* W_dev;      // optional: window length in device memory (then W is its upper bound)
     const int* L_dev;      // optional: compressed tokens in device memory (then nblk is their upper bound, in blocks)
+    int kv_share;          // grid rows (groups of query heads) that share one kv head; 0 is read as 1
     int nblk, nsplit, bps; // compressed blocks, splits over them, blocks per split
     int cap;               // halves of packed values a stage can hold per tensor
     float scale_log2;      // softmax scale * log2(e)

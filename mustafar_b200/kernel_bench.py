@@ -179,6 +179,24 @@ def bench_decode(quick):
         del ks, vs
 
 
+def bench_decode_groups(quick):
+    """Same cache, 1 / 2 / 4 / 8 query heads per kv head: the compressed bytes are read once per kv head whatever the
+    group size, the FMAs grow with it."""
+    B, L = (2, 4096) if quick else (32, 16384)
+    ks, vs = make_cache(B, L, 0.7)
+    Bh = B * HKV
+    kw, vw = synth(Bh, 128, 1, True), synth(Bh, 128, 2, False)
+    hint = max(ks.stage_hint(), vs.stage_hint())
+    for group in (1, 2, 4, 8):
+        q = synth(Bh * group, 1, 3, False).view(Bh * group, D)
+        out = torch.empty_like(q)
+        nbytes = store_bytes(ks) + store_bytes(vs) + 2 * 2 * Bh * 128 * D + 4 * Bh * group * D
+        us = timed_graph(lambda: ops.decode_attention(q, ks, vs, kw, vw, group, out=out, stage_halves=hint))
+        emit("fused decode attention (block, CUDA-graph replay)", us, nbytes, batch=B, kv_len=L, window=128, sparsity=0.7,
+             q_heads_per_kv_head=group)
+    ops.check_device_status()
+
+
 def bench_ops(quick):
     B, L = (2, 4096) if quick else (8, 16384)
     ks, vs = make_cache(B, L, 0.7)
@@ -229,7 +247,7 @@ def main():
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
-    table = {"compress": bench_compress, "compress_fp16": bench_compress_fp16, "decode": bench_decode, "ops": bench_ops, "quant": bench_quant}
+    table = {"compress": bench_compress, "compress_fp16": bench_compress_fp16, "decode_groups": bench_decode_groups, "decode": bench_decode, "ops": bench_ops, "quant": bench_quant}
     for w in a.what.split(","):
         table[w](a.quick)
 

@@ -54,7 +54,7 @@ def reference_layout(store):
     return bmp, nz, idx, off
 
 
-@pytest.mark.parametrize("G,Bh,L", [(1, 3, 256), (4, 2, 512), (4, 3, 2048), (2, 2, 256), (8, 1, 256), (1, 32, 4096)])
+@pytest.mark.parametrize("G,Bh,L", [(1, 3, 256), (4, 2, 512), (4, 3, 2048), (2, 2, 256), (8, 1, 256), (8, 3, 512), (1, 32, 4096)])
 def test_key_formulation(m, G, Bh, L):
     kp, _, ks, _ = build_cache(m, Bh, L, 0.7, 11 + G)
     q = oracle.make_query(Bh * G, seed=5 + L)
@@ -67,7 +67,7 @@ def test_key_formulation(m, G, Bh, L):
     assert float(out[:, 1:].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("G,Bh,L", [(1, 3, 256), (4, 2, 512), (4, 3, 2048), (2, 2, 320), (8, 1, 256), (1, 32, 4096)])
+@pytest.mark.parametrize("G,Bh,L", [(1, 3, 256), (4, 2, 512), (4, 3, 2048), (2, 2, 320), (8, 1, 256), (8, 3, 512), (1, 32, 4096)])
 def test_value_formulation(m, G, Bh, L):
     _, vp, _, vs = build_cache(m, Bh, L, 0.7, 21 + G)
     g = torch.Generator().manual_seed(3 + L)
@@ -88,6 +88,7 @@ def test_value_formulation(m, G, Bh, L):
     (4, 2, 256, 384, 0.7),        # window at its largest (residual + 256)
     (2, 3, 192, 77, 0.7),
     (8, 1, 512, 5, 0.7),
+    (8, 3, 1024, 130, 0.7),       # 8 query heads per kv head: the block kernel runs them as two groups of 4
     (4, 2, 0, 200, 0.7),          # nothing compressed yet
     (1, 2, 64, 0, 0.0),           # unpruned: every tile full, worst-case stage
 ])
