@@ -606,7 +606,7 @@ int launch_combine(const float* ws, int nrec, int G, int normalise, void* out, i
 
 int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G, const void* kwin, const void* vwin,
                          int64_t win_hs, int64_t win_ts, int W, const int* W_dev, float softmax_scale, float* ws,
-                         int rec_index, unsigned* dev_status, cudaStream_t s) {
+                         int rec_index, unsigned* dev_status, cudaStream_t s, bool halves8) {
     if (!kwin || !vwin) return MFAR_ERR_ARG;
     if ((reinterpret_cast<uintptr_t>(kwin) & 15) || (reinterpret_cast<uintptr_t>(vwin) & 15) || (win_hs & 7) || (win_ts & 7))
         return MFAR_ERR_ALIGN;
@@ -625,7 +625,7 @@ int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G,
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.ws = ws;
     p.dev_status = dev_status;
-    return dispatch_decode<MODE_ATTN>(p, G, n_kv_heads, 1, s, false, false);
+    return dispatch_decode<MODE_ATTN>(p, G, n_kv_heads, 1, s, false, halves8);
 }
 
 }  // namespace mfar

@@ -239,10 +239,12 @@ int decode_stream_max_blocks();
 // merge of the split-KV records (normalise = 1) or plain sum (normalise = 0), one CTA per q head
 int launch_combine(const float* ws, int nrec, int G, int normalise, void* out, int64_t out_stride, int n_q_heads,
                    cudaStream_t s);
-// dense recent-token window as split record `rec_index` of a workspace with rec_index + 1 records per kv head
+// dense recent-token window as split record `rec_index` of a workspace with rec_index + 1 records per kv head.
+// halves8: with G = 8 the records are laid out as two groups of 4 query heads per kv head
+// ([kv head * 2 + half][record][4], what the block kernels write) instead of [kv head][record][8]
 int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G, const void* kwin, const void* vwin,
                          int64_t win_hs, int64_t win_ts, int W, const int* W_dev, float softmax_scale, float* ws,
-                         int rec_index, unsigned* dev_status, cudaStream_t s);
+                         int rec_index, unsigned* dev_status, cudaStream_t s, bool halves8 = false);
 
 // Split count of the 64-token-block decode kernels.  The grid is n_kv_heads * ns CTAs of bps = ceil(nblk / ns) blocks.
 // The cost of a candidate follows a model fitted to a measured sweep of ns over batch 1..64 and

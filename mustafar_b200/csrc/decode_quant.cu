@@ -37,6 +37,7 @@ struct QDecodeParams {
     int64_t q_stride;
     int nblk, nsplit, bps, nrec;
     int group32;
+    int kv_share;          // grid rows (groups of query heads) that share one kv head; 0 is read as 1
     float scale_log2;
     float* ws;
     __half* s_out;
@@ -136,7 +137,9 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
     float* alpha_s = reinterpret_cast<float*>(smem + lay.alpha);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int h = blockIdx.y, split = blockIdx.x;
+    // hq numbers the (kv head, group of G query heads) pairs; with kv_share > 1 several of them read the same kv head
+    const int hq = blockIdx.y, split = blockIdx.x;
+    const int h = hq / (p.kv_share > 0 ? p.kv_share : 1);
     const int gi = lane >> 3, kb = lane & 7;
     unsigned sel, mh, ml;
     lane_byte_constants(kb, sel, mh, ml);
@@ -147,7 +150,7 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
     if (MODE != MODE_VALUE) {
         for (int i = tid; i < kD * G; i += kQThreads) {
             const int c = i / G, g = i % G;
-            qh[i] = __half2float(p.q[(static_cast<int64_t>(h) * G + g) * p.q_stride + c]);
+            qh[i] = __half2float(p.q[(static_cast<int64_t>(hq) * G + g) * p.q_stride + c]);
         }
     }
 
@@ -246,7 +249,7 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
         if (MODE == MODE_VALUE) {
             for (int g = warp; g < G; g += kQWarps) {
                 const unsigned pv = *reinterpret_cast<const unsigned*>(
-                    p.p_in + (static_cast<int64_t>(h) * G + g) * p.p_stride + static_cast<int64_t>(blk0 + i) * 64 + 2 * lane);
+                    p.p_in + (static_cast<int64_t>(hq) * G + g) * p.p_stride + static_cast<int64_t>(blk0 + i) * 64 + 2 * lane);
                 ps[(2 * lane) * G + g] = __half2float(__ushort_as_half(static_cast<unsigned short>(pv & 0xffffu)));
                 ps[(2 * lane + 1) * G + g] = __half2float(__ushort_as_half(static_cast<unsigned short>(pv >> 16)));
             }
@@ -263,7 +266,7 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
                         s1 += t.y;
                     }
                     if (MODE == MODE_KEY) {
-                        *reinterpret_cast<__half2*>(p.s_out + (static_cast<int64_t>(h) * G + g) * p.s_stride +
+                        *reinterpret_cast<__half2*>(p.s_out + (static_cast<int64_t>(hq) * G + g) * p.s_stride +
                                                     static_cast<int64_t>(blk0 + i) * 64 + 2 * lane) = __floats2half2_rn(s0, s1);
                     } else {
                         s0 *= p.scale_log2;
@@ -325,7 +328,7 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
         }
     }
     __syncthreads();
-    float* rec = p.ws + ((static_cast<int64_t>(h) * p.nrec + split) * G) * kPartialStride;
+    float* rec = p.ws + ((static_cast<int64_t>(hq) * p.nrec + split) * G) * kPartialStride;
     for (int idx = tid; idx < G * kD; idx += kQThreads) {
         const int g = idx / kD, c = idx % kD;
         float s = 0.f;
@@ -376,7 +379,13 @@ static int dispatch_q(const QDecodeParams& p, int G, int bits, int n_kv_heads, c
         MFAR_QCASE(1)
         MFAR_QCASE(2)
         MFAR_QCASE(4)
-        MFAR_QCASE(8)
+        case 8: {
+            // 64 accumulators per phase spill; two CTAs of 4 query heads each share the kv head instead
+            // (records then lie as [kv head * 2 + half][record][4]: combine with G = 4)
+            QDecodeParams p2 = p;
+            p2.kv_share = 2;
+            return dispatch_q<MODE>(p2, 4, bits, 2 * n_kv_heads, s);
+        }
         default: return MFAR_ERR_ARG;
     }
 #undef MFAR_QCASE
@@ -458,7 +467,7 @@ extern "C" int mfar_value_output_quant(const void* probs, int64_t probs_stride, 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     r = dispatch_q<MODE_VALUE>(p, group, bits, n_kv_heads, s);
     if (r) return r;
-    return launch_combine(p.ws, p.nrec, group, 0, out, out_stride, n_kv_heads * group, s);
+    return launch_combine(p.ws, p.nrec, group == 8 ? 4 : group, 0, out, out_stride, n_kv_heads * group, s);
 }
 
 extern "C" int mfar_decode_attention_quant(
@@ -506,8 +515,8 @@ extern "C" int mfar_decode_attention_quant(
     }
     if (window > 0) {
         r = launch_window_record(q, q_stride, n_kv_heads, group, k_window, v_window, win_head_stride, win_token_stride,
-                                 window, nullptr, softmax_scale, p.ws, p.nsplit, dev_status, s);
+                                 window, nullptr, softmax_scale, p.ws, p.nsplit, dev_status, s, true);
         if (r) return r;
     }
-    return launch_combine(p.ws, p.nrec, group, 1, out, out_stride, n_kv_heads * group, s);
+    return launch_combine(p.ws, p.nrec, group == 8 ? 4 : group, 1, out, out_stride, n_kv_heads * group, s);
 }

@@ -73,7 +73,7 @@ def build(m, Bh, L, s, bits, group, seed):
 
 
 @pytest.mark.parametrize("G,Bh,L,s,bits,group", [
-    (1, 3, 256, 0.7, 2, 64), (4, 2, 512, 0.5, 2, 64), (4, 2, 1024, 0.7, 2, 64), (8, 1, 256, 0.7, 2, 64),
+    (1, 3, 256, 0.7, 2, 64), (4, 2, 512, 0.5, 2, 64), (4, 2, 1024, 0.7, 2, 64), (8, 1, 256, 0.7, 2, 64), (8, 3, 512, 0.7, 2, 64),
     (4, 2, 256, 0.7, 4, 64), (4, 2, 256, 0.5, 2, 32), (2, 2, 192, 0.5, 4, 32),
 ])
 def test_quant_ops_vs_dequantise_then_dense(m, G, Bh, L, s, bits, group):
@@ -109,6 +109,7 @@ def test_quant_ops_vs_dequantise_then_dense(m, G, Bh, L, s, bits, group):
 @pytest.mark.parametrize("G,Bh,L,W,s,bits,group", [
     (4, 8, 2048, 128, 0.7, 2, 64), (4, 2, 512, 200, 0.5, 2, 64), (1, 4, 256, 0, 0.7, 2, 64),
     (4, 2, 256, 128, 0.7, 4, 64), (4, 2, 256, 128, 0.5, 2, 32), (4, 2, 0, 130, 0.7, 2, 64),
+    (8, 3, 512, 130, 0.7, 2, 64), (8, 2, 256, 0, 0.7, 4, 64),      # 8 query heads per kv head: two groups of 4
 ])
 def test_fused_quant_attention(m, G, Bh, L, W, s, bits, group):
     if L:
