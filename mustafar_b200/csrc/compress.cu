@@ -155,10 +155,10 @@ __global__ void __launch_bounds__(128, MFAR_COMPRESS_MIN_CTAS) compress_kernel(C
             unsigned o = 2 * excl_tile;
             const unsigned end = 2 * incl;
             const int c = tid;
-#pragma unroll 8
+#pragma unroll
             for (int i = 0; i < 32; ++i)
                 if ((hi >> (31 - i)) & 1u) ps[o++] = xs[i * kXsStride + c];
-#pragma unroll 8
+#pragma unroll
             for (int i = 0; i < 32; ++i)
                 if ((lo >> (31 - i)) & 1u) ps[o++] = xs[(32 + i) * kXsStride + c];
             while (o < end) ps[o++] = 0;

@@ -174,10 +174,10 @@ __global__ void __launch_bounds__(128) compress_quant_kernel(QuantParams p) {
     if (KIND == MFAR_KIND_KEY) {
         unsigned o = voff;
         const int c = tid;
-#pragma unroll 8
+#pragma unroll
         for (int i = 0; i < 32; ++i)
             if ((hi >> (31 - i)) & 1u) vals[o++] = xs[i * kXsStride + c];
-#pragma unroll 8
+#pragma unroll
         for (int i = 0; i < 32; ++i)
             if ((lo >> (31 - i)) & 1u) vals[o++] = xs[(32 + i) * kXsStride + c];
     } else {
