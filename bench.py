@@ -6,9 +6,11 @@
 
 One "step" = one decode-attention layer pass (q.K^T over the compressed cache + dense
 window, softmax, P.V) for a batch of B sequences with the Llama-3-8B head shape
-(32 query heads, 8 kv heads, head_dim 128).  Workload = BASELINE config "batched decode
-sparse attention" at its largest point (B=64, L=32768, window 128, 70 % sparsity);
-inputs are seeded synthetic tensors (K, V ~ N(0,1), four K outlier channels x10).
+(32 query heads, 8 kv heads, head_dim 128).  Default workload = batched decode sparse attention
+at its largest point (B=64, L=32768, window 128, 70 % sparsity); inputs are seeded synthetic
+tensors (K, V ~ N(0,1), four K outlier channels x10).  After the timed region the step's output
+is checked, for a sample of kv heads, against the CPU oracle fed with those heads' slices of the
+very cache that was timed ("parity_check"; a failure makes the run exit non-zero).
 
 Prints ONE JSON line (rank 0).  `value` = sequences * steps / device time, i.e. decode
 tokens per second through one attention layer, whole job over all ranks (batch-sharded
@@ -46,7 +48,7 @@ def parse():
     ap.add_argument("--sparsity", type=float, default=0.7)
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--variant", default="auto", choices=["auto", "block", "block32", "superblock", "stream", "stream16"])
+    ap.add_argument("--parity-heads", type=int, default=4, help="kv heads checked against the CPU oracle after timing")
     return ap.parse_args()
 
 
@@ -152,6 +154,41 @@ def algorithmic_bytes(ks, vs, window, batch):
     return total
 
 
+def traffic_estimate(alg_bytes):
+    """DRAM traffic of one launch: the read + written bytes per algorithmic byte that ncu measured on a smaller
+    case of the same kernel (traffic grows with the tokens read), times this launch's algorithmic bytes."""
+    p = os.path.join(ROOT, "profiles", "decode_attn_traffic.txt")
+    try:
+        d = dict(line.split(":", 1) for line in open(p) if ":" in line and not line.startswith("#"))
+        return alg_bytes * float(d["dram_bytes"]) / float(d["algorithmic_bytes"])
+    except Exception:
+        return None
+
+
+def parity_check(q, out, ks, vs, kw, vw, n_heads, tol=2e-3):
+    """Checks the timed configuration itself: for a sample of kv heads, their slices of the compressed cache are
+    copied to the host, decompressed by the oracle, and the oracle's fp32 attention over [decompressed ; window]
+    is compared with the kernel's output for the G query heads of each sampled kv head."""
+    import oracle
+    Bh, L = ks.n_heads, ks.tokens
+    n_heads = max(1, min(n_heads, Bh))
+    heads = sorted({int(round(i * (Bh - 1) / max(1, n_heads - 1))) for i in range(n_heads)})
+    T = ks.tiles
+    worst = 0.0
+    for h in heads:
+        dense = []
+        for st, fn in ((ks, oracle.decompress_key_ref), (vs, oracle.decompress_value_ref)):
+            bmp = st.bitmaps[h:h + 1, :T].cpu().numpy()
+            acc = st.accum[h:h + 1, :T + 1].cpu().numpy()
+            n = 2 * int(acc[0, -1])
+            packed = [st.nz[h, :n].cpu().numpy()]
+            dense.append(torch.from_numpy(fn(bmp, acc, packed, L)))
+        want = oracle.decode_attention_ref(q[h * G:(h + 1) * G].cpu(), dense[0], dense[1], kw[h:h + 1].cpu(), vw[h:h + 1].cpu(), G)
+        worst = max(worst, oracle.rel_l2(out[h * G:(h + 1) * G].float().cpu(), want))
+    return {"heads": len(heads), "kv_heads_checked": heads, "rel_l2": worst, "tol": tol, "ok": bool(worst < tol),
+            "against": "oracle.decode_attention_ref on the oracle-decompressed cache slices of the sampled heads"}
+
+
 # ------------------------------------------------------------------------------------------ CPU baseline
 def cpu_baseline(kv_len, window, sparsity, budget_s, steps=None, warmup=3):
     """The reference's torch path on the host cores (oracle port): dense
@@ -235,9 +272,11 @@ def main():
     out = torch.empty(Bq, D, dtype=torch.float16, device=dev)
     hint = max(ks.stage_hint(), vs.stage_hint())
     alg_bytes = algorithmic_bytes(ks, vs, a.window, a.batch)
+    _, ws_bytes = ops.plan(a.batch * HKV, a.kv_len, a.window, G)
+    ws = ops.new_workspace(dev, ws_bytes)
 
     def step():
-        ops.decode_attention(q, ks, vs, kw, vw, G, out=out, stage_halves=hint, variant=a.variant)
+        ops.decode_attention(q, ks, vs, kw, vw, G, out=out, stage_halves=hint, workspace=ws)
 
     def barrier():
         torch.cuda.synchronize()
@@ -257,8 +296,10 @@ def main():
             ev[i + 1].record()
         torch.cuda.synchronize()
     total_ms = ev[0].elapsed_time(ev[-1])
-    per_launch_ms = sum(ev[i].elapsed_time(ev[i + 1]) for i in range(a.steps)) / a.steps
+    step_ms = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(a.steps))
+    per_launch_ms = sum(step_ms) / a.steps
     barrier()
+    parity = parity_check(q, out, ks, vs, kw, vw, a.parity_heads) if rank == 0 else None
 
     # end to end through the public API with host buffers: q from pinned memory, result back to the host
     q_host = q.cpu().pin_memory()
@@ -267,7 +308,7 @@ def main():
 
     def e2e_step():
         q_dev.copy_(q_host, non_blocking=True)
-        ops.decode_attention(q_dev, ks, vs, kw, vw, G, out=out, stage_halves=hint, variant=a.variant)
+        ops.decode_attention(q_dev, ks, vs, kw, vw, G, out=out, stage_halves=hint, workspace=ws)
         out_host.copy_(out, non_blocking=True)
 
     for _ in range(3):
@@ -297,14 +338,16 @@ def main():
             "clocks": clocks.summary(),
             "e2e": {"value": world * a.batch * a.steps / (e2e_ms * 1e-3), "unit": "tok/s/layer",
                     "h2d_bytes_per_step": q.numel() * 2, "d2h_bytes_per_step": out.numel() * 2},
-            "gpu_launches": (3 if a.variant.startswith("stream") or a.variant == "superblock" else 2) * a.steps,
+            "step_ms": {"min": step_ms[0], "median": step_ms[len(step_ms) // 2], "max": step_ms[-1]},
+            "gpu_launches": a.steps,
+            "parity_check": parity,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": which, "frac_of_nominal_8000": achieved / 8000.0,
                          "algorithmic_bytes_per_launch": alg_bytes,
-                         # dram__bytes_read+write of one launch in the ncu capture of the B=16, L=8192 case
-                         # (262.8 MB read + written for 256.9 MB algorithmic), scaled by the units of this launch
-                         "traffic": alg_bytes * (262.8 / 256.9),
-                         "kernel": "decode kernel, variant %s (+ combine_kernel, <1 %% of the step)" % a.variant},
+                         # dram bytes read + written per algorithmic byte in the ncu capture of a smaller case
+                         # (profiles/decode_attn_traffic.txt), scaled by the units of this launch
+                         "traffic": traffic_estimate(alg_bytes),
+                         "kernel": "decode_attn_kernel (one launch per step: decode + merge of the split records)"},
         }
         if not a.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(a.kv_len, a.window, a.sparsity, a.cpu_seconds)
@@ -312,6 +355,8 @@ def main():
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+    if parity is not None and not parity["ok"]:
+        raise SystemExit(f"parity check failed: {parity}")
 
 
 if __name__ == "__main__":

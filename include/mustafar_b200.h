@@ -45,10 +45,6 @@ typedef enum {
 #define MFAR_DEV_BADMETA 4u    /* offsets in the cache are inconsistent           */
 
 enum { MFAR_KIND_KEY = 0, MFAR_KIND_VALUE = 1 };
-enum { MFAR_DECODE_FORCE_BLOCK = 1, MFAR_DECODE_FORCE_SUPERBLOCK = 2, MFAR_DECODE_FORCE_STREAM = 4,
-       MFAR_DECODE_FP16_COEF = 8 /* stream kernel: q and the probabilities enter the FMA as fp16 */,
-       MFAR_DECODE_FP32_COEF = 16 /* block kernel: keep the probabilities in fp32 (default: rounded to fp16
-                                     before P.V, as the reference model does, one mixed-precision FMA per value) */ };
 
 int mfar_version(void);
 const char* mfar_status_string(int status);
@@ -76,8 +72,10 @@ const char* mfar_status_string(int status);
  *              nz + 8*nz_offset[h] halves (nz_offset device int32, uint4 units,
  *              the reference's NZ_Offset) or, when nz_offset is NULL, at
  *              nz + h*nz_head_stride halves (multiple of 8).
- * nz_capacity  halves available per head (bounds check; overflow sets
- *              MFAR_DEV_CAPACITY and the head's remaining blocks are skipped).
+ * nz_capacity  halves available per head (bounds check; a 64-token block that would not fit
+ *              sets MFAR_DEV_CAPACITY and its values are dropped: bitmaps and accum are
+ *              still written and later blocks carry on, so the cache is unusable and the
+ *              caller has to look at dev_status).
  * scratch      device, mfar_compress_scratch_bytes() bytes, 16-byte aligned;
  *              cleared by this call (no need to pre-zero).
  * dev_status   device uint32 or NULL.
@@ -149,18 +147,25 @@ int mfar_compress_quant(const void* x, int64_t x_head_stride, int64_t x_token_st
 /* ------------------------------------------------------------------------- *
  * Decode over the fp16 compressed cache.  Common arguments:
  *
- * q             device fp16, query of q-head i at q + i*q_stride (128 halves);
+ * q             device fp16, query of q-head i at q + i*q_stride (128 halves), 4-byte aligned, q_stride even;
  *               q-head i uses kv head i / group  (kernel/csrc/SpMM_Kernel.cuh:258-265).
  * n_kv_heads    B * Hkv;  group = Hq / Hkv in {1, 2, 4, 8}.
  * bitmaps/accum/nz/nz_offset/..._head_stride   the cache as written by
  *               mfar_compress_fp16 (bmp_head_stride even; bitmaps and nz 16-byte
  *               aligned); n_tokens = compressed tokens, multiple of 64.
+ * nz_extent     halves addressable from nz (the whole buffer, all heads), or 0 when unknown.  The
+ *               kernels check every 64-token block's packed range before copying it: start and
+ *               size 16-byte aligned, size within the stage, end within nz_extent; a block that
+ *               fails sets MFAR_DEV_BADMETA and its values are not read (no fault).
  * stage_halves  upper bound on the packed halves of any 64-token block of one
  *               tensor (sizes the shared-memory ring); 0 = worst case 8192.  A
  *               block larger than the bound sets MFAR_DEV_BADMETA.
  * ------------------------------------------------------------------------- */
 
-/* Split count and workspace size the decode entry points will use. */
+/* Split count and workspace size the decode entry points will use.  The first 64 KiB of a workspace are arrival
+ * counters of the fused attention (one per kv head; the split records of every entry point start behind them):
+ * they must be ZERO before the first call that uses the buffer; every call leaves them zero again (also after a
+ * bounded wait gave up).  Calls that could overlap on the GPU need workspaces of their own. */
 int mfar_decode_plan(int n_kv_heads, int n_tokens, int window, int nsplit_hint, int* nsplit_out,
                      size_t* workspace_bytes, int group);
 
@@ -172,17 +177,16 @@ int mfar_decode_plan(int n_kv_heads, int n_tokens, int window, int nsplit_hint, 
  * (elements, multiples of 8); window may be 0.  workspace: mfar_decode_plan bytes.
  * window_len_dev: NULL, or a device int32 holding the current window length (<= window, which is then the
  * capacity): lets a launch captured in a CUDA graph be replayed while the window grows.
- * nsplit 0 = automatic.  flags: 0, or one of MFAR_DECODE_FORCE_* to pin the kernel variant
- * (64-token block kernel / 256-token superblock kernel) instead of the size heuristic. */
+ * nsplit 0 = automatic.  One kernel launch: the CTA that finishes a kv head last merges its split records. */
 int mfar_decode_attention_fp16(
     const void* q, int64_t q_stride, int n_kv_heads, int group,
     const int64_t* k_bitmaps, int64_t k_bmp_head_stride, const int32_t* k_accum, int64_t k_acc_head_stride,
-    const void* k_nz, const int32_t* k_nz_offset, int64_t k_nz_head_stride,
+    const void* k_nz, const int32_t* k_nz_offset, int64_t k_nz_head_stride, int64_t k_nz_extent,
     const int64_t* v_bitmaps, int64_t v_bmp_head_stride, const int32_t* v_accum, int64_t v_acc_head_stride,
-    const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride,
+    const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride, int64_t v_nz_extent,
     int n_tokens, const void* k_window, const void* v_window, int64_t win_head_stride, int64_t win_token_stride,
     int window, const int32_t* window_len_dev, float softmax_scale, void* out, int64_t out_stride, void* workspace,
-    size_t workspace_bytes, int nsplit, int stage_halves, int flags, uint32_t* dev_status, void* stream);
+    size_t workspace_bytes, int nsplit, int stage_halves, uint32_t* dev_status, void* stream);
 
 /* scores[i*scores_stride + t] = sum_c K~[i/group][t][c] * q[i][c]  (fp32 accumulate, fp16 store).
  * Replaces mustafar_key_formulation -> Key_SplitK_API -> Key_Kernel
@@ -191,8 +195,8 @@ int mfar_decode_attention_fp16(
 int mfar_key_scores_fp16(const void* q, int64_t q_stride, int n_kv_heads, int group,
                          const int64_t* bitmaps, int64_t bmp_head_stride, const int32_t* accum,
                          int64_t acc_head_stride, const void* nz, const int32_t* nz_offset,
-                         int64_t nz_head_stride, int n_tokens, void* scores, int64_t scores_stride,
-                         int stage_halves, uint32_t* dev_status, void* stream);
+                         int64_t nz_head_stride, int64_t nz_extent, int n_tokens, void* scores,
+                         int64_t scores_stride, int stage_halves, uint32_t* dev_status, void* stream);
 
 /* out[i*out_stride + c] = sum_t V~[i/group][t][c] * probs[i*probs_stride + t].
  * Replaces mustafar_value_formulation -> Value_SplitK_API -> Value_Kernel (+SplitK_Reduction)
@@ -201,9 +205,9 @@ int mfar_key_scores_fp16(const void* q, int64_t q_stride, int n_kv_heads, int gr
 int mfar_value_output_fp16(const void* probs, int64_t probs_stride, int n_kv_heads, int group,
                            const int64_t* bitmaps, int64_t bmp_head_stride, const int32_t* accum,
                            int64_t acc_head_stride, const void* nz, const int32_t* nz_offset,
-                           int64_t nz_head_stride, int n_tokens, void* out, int64_t out_stride,
-                           void* workspace, size_t workspace_bytes, int nsplit, int stage_halves,
-                           uint32_t* dev_status, void* stream);
+                           int64_t nz_head_stride, int64_t nz_extent, int n_tokens, void* out,
+                           int64_t out_stride, void* workspace, size_t workspace_bytes, int nsplit,
+                           int stage_halves, uint32_t* dev_status, void* stream);
 
 /* ------------------------------------------------------------------------- *
  * Decode over the quantised cache written by mfar_compress_quant (bits in {2,4},
@@ -223,8 +227,8 @@ int mfar_key_scores_quant(const void* q, int64_t q_stride, int n_kv_heads, int g
 
 /* Replaces mustafar_value_formulation_quant and ..._decode_n1 -> Value_SplitK_API_Quant -> Value_Kernel_Quant
  * (kernel_quant/kernel_wrapper/mustafar_wrapper_quant.cu:217-457, kernel_quant/csrc/SpMM_API_Quant.cu:342-573,
- *  kernel_quant/csrc/SpMM_Kernel_Quant.cuh:510-735).  workspace: n_kv_heads * splits * group * 132 floats,
- *  splits <= max(1, n_tokens / 128) unless nsplit is given. */
+ *  kernel_quant/csrc/SpMM_Kernel_Quant.cuh:510-735).  workspace: the 64 KiB of counters described at mfar_decode_plan
+ *  (left untouched) + n_kv_heads * splits * group * 132 floats, splits <= max(1, n_tokens / 128) unless nsplit is given. */
 int mfar_value_output_quant(const void* probs, int64_t probs_stride, int n_kv_heads, int group,
                             const int64_t* bitmaps, int64_t bmp_head_stride, const int32_t* tile_offsets,
                             const void* scales, const void* zeros, int64_t meta_head_stride,
@@ -249,18 +253,18 @@ int mfar_decode_attention_quant(
  * compressed tokens is read from n_tokens_dev (int32 on the device, a multiple of 64) when the kernel runs;
  * max_tokens (a multiple of 64) bounds it and sizes the grid, the plan (mfar_decode_plan with max_tokens) and
  * the workspace.  stage_halves must cover the largest 64-token block that will ever be appended
- * (64 * kept values per token + 7 * 128 of padding is always enough).  Block kernel only: the superblock /
- * stream flags are refused.  No reference counterpart (the reference re-launches with host-side lengths,
+ * (64 * kept values per token + 7 * 128 of padding is enough unless tokens have more than three ties at the
+ * pruning threshold; a larger block sets MFAR_DEV_BADMETA when it is decoded).  No reference counterpart (the reference re-launches with host-side lengths,
  * models/llama_mustafar_kernel.py:391-438). */
 int mfar_decode_attention_fp16_dyn(
     const void* q, int64_t q_stride, int n_kv_heads, int group,
     const int64_t* k_bitmaps, int64_t k_bmp_head_stride, const int32_t* k_accum, int64_t k_acc_head_stride,
-    const void* k_nz, const int32_t* k_nz_offset, int64_t k_nz_head_stride,
+    const void* k_nz, const int32_t* k_nz_offset, int64_t k_nz_head_stride, int64_t k_nz_extent,
     const int64_t* v_bitmaps, int64_t v_bmp_head_stride, const int32_t* v_accum, int64_t v_acc_head_stride,
-    const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride,
+    const void* v_nz, const int32_t* v_nz_offset, int64_t v_nz_head_stride, int64_t v_nz_extent,
     int max_tokens, const int32_t* n_tokens_dev, const void* k_window, const void* v_window, int64_t win_head_stride,
     int64_t win_token_stride, int window, const int32_t* window_len_dev, float softmax_scale, void* out,
-    int64_t out_stride, void* workspace, size_t workspace_bytes, int nsplit, int stage_halves, int flags,
+    int64_t out_stride, void* workspace, size_t workspace_bytes, int nsplit, int stage_halves,
     uint32_t* dev_status, void* stream);
 
 /* ---- decode-step glue (no counterpart in the reference's extensions: its model file does these with torch ops) ----
@@ -279,11 +283,12 @@ int mfar_add_rmsnorm_f16(void* x, const void* delta, const void* weight, void* o
  * (models/llama_mustafar_kernel.py:373-374); q goes to q_out [batch*n_q_heads, 128]; k and v go into the dense
  * windows [batch*n_kv_heads][slot] (the torch.cat of :391 and :430 without the copy).  Position and slot are read from
  * pos_dev / slot_dev (int32 on the device) when those are not NULL, so that a captured CUDA graph can be replayed
- * while they advance; else from pos / slot. */
+ * while they advance; else from pos / slot.  window_capacity = token slots per window head: a slot outside
+ * [0, window_capacity) writes nothing to the windows and sets MFAR_DEV_BADMETA in *dev_status (device uint32 or NULL). */
 int mfar_rope_append_f16(const void* qkv, const float* inv_freq, const int32_t* pos_dev, int pos,
                          const int32_t* slot_dev, int slot, int batch, int n_q_heads, int n_kv_heads,
                          void* q_out, void* k_window, void* v_window, int64_t win_head_stride,
-                         int64_t win_token_stride, void* stream);
+                         int64_t win_token_stride, int window_capacity, uint32_t* dev_status, void* stream);
 
 /* out[r, j] = fp16(silu(gate_up[r, j])) * gate_up[r, width + j], gate_up [rows, 2*width] (HF LlamaMLP). */
 int mfar_silu_mul_f16(const void* gate_up, void* out, int64_t rows, int width, void* stream);

@@ -9,8 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# MUSTAFAR_B200_LIB points at an alternative build of the same ABI (kernel experiments)
-LIB_PATH = os.environ.get("MUSTAFAR_B200_LIB") or os.path.join(_HERE, "libmustafar_b200.so")
+LIB_PATH = os.path.join(_HERE, "libmustafar_b200.so")
 
 OK = 0
 DEV_CAPACITY, DEV_TIMEOUT, DEV_BADMETA = 1, 2, 4
@@ -31,18 +30,18 @@ SIGNATURES = {
                                    _i64, _i64, _vp, _i64, _i64, _vp, _vp, _sz, _vp, _vp]),
     "mfar_decode_plan": (_i32, [_i32, _i32, _i32, _i32, C.POINTER(_i32), C.POINTER(_sz), _i32]),
     "mfar_decode_attention_fp16": (_i32, [_vp, _i64, _i32, _i32,
-                                          _vp, _i64, _vp, _i64, _vp, _vp, _i64,
-                                          _vp, _i64, _vp, _i64, _vp, _vp, _i64,
+                                          _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64,
+                                          _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64,
                                           _i32, _vp, _vp, _i64, _i64, _i32, _vp, _f32, _vp, _i64, _vp, _sz,
-                                          _i32, _i32, _i32, _vp, _vp]),
+                                          _i32, _i32, _vp, _vp]),
     "mfar_decode_attention_fp16_dyn": (_i32, [_vp, _i64, _i32, _i32,
-                                              _vp, _i64, _vp, _i64, _vp, _vp, _i64,
-                                              _vp, _i64, _vp, _i64, _vp, _vp, _i64,
+                                              _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64,
+                                              _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64,
                                               _i32, _vp, _vp, _vp, _i64, _i64, _i32, _vp, _f32, _vp, _i64, _vp, _sz,
-                                              _i32, _i32, _i32, _vp, _vp]),
-    "mfar_key_scores_fp16": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32,
+                                              _i32, _i32, _vp, _vp]),
+    "mfar_key_scores_fp16": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i32,
                                     _vp, _i64, _i32, _vp, _vp]),
-    "mfar_value_output_fp16": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i32,
+    "mfar_value_output_fp16": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _i64, _vp, _vp, _i64, _i64, _i32,
                                       _vp, _i64, _vp, _sz, _i32, _i32, _vp, _vp]),
     "mfar_key_scores_quant": (_i32, [_vp, _i64, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _i64, _vp, _i64, _i32, _i32, _i32,
                                      _vp, _i64, _vp, _vp]),
@@ -55,7 +54,8 @@ SIGNATURES = {
                                            _vp, _vp, _i64, _i64, _i32,
                                            _f32, _vp, _i64, _vp, _sz, _i32, _vp, _vp]),
     "mfar_add_rmsnorm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp]),
-    "mfar_rope_append_f16": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i64, _i64, _vp]),
+    "mfar_rope_append_f16": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _vp,
+                                    _vp]),
     "mfar_silu_mul_f16": (_i32, [_vp, _vp, _i64, _i32, _vp]),
 }
 

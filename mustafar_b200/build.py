@@ -20,7 +20,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libmustafar_b200.so")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
-FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--use_fast_math=false"]
+FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
 
 
 def _nvcc() -> str:
@@ -38,19 +38,12 @@ def _newest_header() -> float:
     return t
 
 
-def build(force: bool = False, verbose: bool = False, defines=(), tag: str = "") -> str:
-    """``defines`` / ``tag`` build an experimental variant (``-DNAME=VALUE``) into
-    libmustafar_b200<tag>.so with its own object directory; the default build takes neither."""
-    global OBJ, LIB
+def build(force: bool = False, verbose: bool = False) -> str:
     nvcc = _nvcc()
-    if tag:
-        OBJ = os.path.join(HERE, "build" + tag)
-        LIB = os.path.join(HERE, f"libmustafar_b200{tag}.so")
     os.makedirs(OBJ, exist_ok=True)
     srcs = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
     hdr_t = _newest_header()
-    flags = [f for f in FLAGS if f != "--use_fast_math=false"]
-    flags = flags + [f"-D{d}" for d in defines]
+    flags = list(FLAGS)
     if verbose:
         flags = flags + ["-Xptxas", "-v"]
     jobs = []
@@ -86,7 +79,5 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
-    ap.add_argument("-D", dest="defines", action="append", default=[])
-    ap.add_argument("--tag", default="")
     a = ap.parse_args()
-    print(build(a.force, a.verbose, a.defines, a.tag))
+    print(build(a.force, a.verbose))

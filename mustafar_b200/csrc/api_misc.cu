@@ -1,5 +1,21 @@
-// Version / status strings of the C ABI.
+// Version / status strings of the C ABI, and the cached device query.
 #include "common.cuh"
+
+namespace mfar {
+
+int device_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+}  // namespace mfar
 
 extern "C" int mfar_version(void) { return 100; }
 

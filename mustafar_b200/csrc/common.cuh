@@ -54,6 +54,9 @@ __device__ __forceinline__ unsigned smem_u32(const void* p) {
     return static_cast<unsigned>(__cvta_generic_to_shared(p));
 }
 
+// multiprocessors of the current device (queried once per device; api_misc.cu)
+int device_sm_count();
+
 inline int launch_status() { return cudaGetLastError() == cudaSuccess ? MFAR_OK : MFAR_ERR_LAUNCH; }
 
 }  // namespace mfar

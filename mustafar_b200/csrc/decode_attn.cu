@@ -1,0 +1,541 @@
+// Fused decode attention over the bitmap + packed-fp16 cache:
+//   q.K^T over the compressed tokens, online softmax, P.V, split-KV partial records, and the merge of the
+//   records by the CTA that finishes a kv head last (one launch per call); one extra CTA per kv head handles
+//   the dense recent-token window.
+//
+// A CTA (4 warps) walks a range of 64-token blocks of ONE kv head and serves all G query heads that share it, so
+// the compressed bytes are read once.  Per block the two bitmap arrays (1 KiB each) and the two packed-value
+// ranges travel into a 2-stage shared-memory ring by 1-D bulk copies (cp.async.bulk + mbarrier, no multicast),
+// issued by one thread one block ahead.
+//
+// Decode: a lane owns one BYTE (8 positions) of the bitmaps of TWO tiles.  The rank of the byte's first position is
+// the popcount of the bitmap bits before it; every set bit then takes the next packed half from shared memory
+// (a predicated 16-bit load), absent positions stay zero, and the two tiles' values at the same position are packed
+// into one 32-bit register.  Those registers ARE fragments of mma.sync.m16n8k16 (fp16 in, fp32 accumulate):
+//   K phase   S[token][head]   = sum_c K[token][c] q[c][head]     rows = tokens,   k = channels (= K tiles)
+//   V phase   O[channel][head] = sum_t V[t][channel] p[t][head]   rows = channels, k = tokens   (= V tiles)
+// In both phases the position inside a tile is the row and the tile index is the contraction index, which is exactly
+// how the A fragment spreads over a warp (row = lane / 4, k pair = lane % 4), so no transposition is needed.  The
+// query heads (up to 8) are the n dimension.  The multiply-accumulate of a 64-token block is 64 tensor-core
+// instructions per CTA; what remains, and what bounds the kernel, is the shared-memory traffic of the
+// predicated loads.
+#include "decode_common.cuh"
+
+namespace mfar {
+
+constexpr int kAWarps = 4;
+constexpr int kAThreads = kAWarps * 32;
+constexpr int kAStages = 2;
+constexpr int kPsStride = 72;      // halves per probability row: 36 words, so the 8 head rows fall in different banks
+constexpr int kPlaneStride = 72;   // floats per (warp, head) score plane
+
+__host__ __device__ inline size_t attn_stage_bytes(int cap) {
+    return 2 * (1024 + (static_cast<size_t>(cap) + kSlackHalves) * 2);
+}
+
+struct AttnLayout {
+    size_t stages, bars, ps, red, alpha, koff, voff, kblk, vblk, total;
+    size_t s_kbm, s_vbm, s_kval, s_vval;
+    __host__ __device__ AttnLayout(int cap, int G) {
+        s_kbm = 0;
+        s_vbm = 1024;
+        s_kval = 2048;
+        s_vval = 2048 + (static_cast<size_t>(cap) + kSlackHalves) * 2;
+        size_t o = 0;
+        stages = o; o += kAStages * attn_stage_bytes(cap);
+        bars = o;   o += 64;
+        ps = o;     o += 8 * kPsStride * 2;
+        red = o;    o += static_cast<size_t>(kAWarps) * G * kD * 4;   // score planes, later the output reduction
+        alpha = o;  o += 64;
+        koff = o;   o += 2 * 128 * 4;
+        voff = o;   o += 2 * 128 * 4;
+        kblk = o;   o += (kMaxBlocksPerSplit + 4) * 4;
+        vblk = o;   o += (kMaxBlocksPerSplit + 4) * 4;
+        total = o;
+    }
+};
+
+__device__ __forceinline__ void mma16816(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                         unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Byte `sel` (8 positions) of two tiles -> 8 registers, low half = tile A, high half = tile B, zero where the bit
+// is clear.  bm = {lo A, hi A, lo B, hi B}; va / vb point at the tiles' packed values.
+__device__ __forceinline__ void expand_pair(uint4 bm, const unsigned short* va, const unsigned short* vb, unsigned sel,
+                                            unsigned mh, unsigned ml, unsigned (&r)[8]) {
+    const unsigned ba = __byte_perm(bm.x, bm.y, sel), bb = __byte_perm(bm.z, bm.w, sel);
+    const unsigned short* pa[2];
+    const unsigned short* pb[2];
+    pa[0] = va + (__popc(bm.y & mh) + __popc(bm.x & ml));
+    pb[0] = vb + (__popc(bm.w & mh) + __popc(bm.z & ml));
+    pa[1] = pa[0] + __popc(ba & 0xf0u);
+    pb[1] = pb[0] + __popc(bb & 0xf0u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        unsigned lo = 0, hi = 0;
+        if (ba & (0x80u >> i)) { lo = *pa[i / 4]; ++pa[i / 4]; }
+        if (bb & (0x80u >> i)) { hi = *pb[i / 4]; ++pb[i / 4]; }
+        r[i] = __byte_perm(lo, hi, 0x5410);
+    }
+}
+
+__device__ __forceinline__ unsigned ldg_nc_u32(const void* p) {
+    unsigned v;
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ unsigned ldg_nc_u16(const void* p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float ldcg_f32(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
+// record of (kv head h, split, query head g) inside the workspace
+__device__ __forceinline__ float* record_ptr(const DecodeParams& p, int G, int h, int split, int g) {
+    const int rg = p.rec_group;
+    const int sets = G / rg;
+    return p.ws + ((static_cast<int64_t>(h * sets + g / rg) * p.nrec + split) * rg + (g % rg)) * kPartialStride;
+}
+
+template <int G>
+__global__ void __launch_bounds__(kAThreads, 4) decode_attn_kernel(DecodeParams p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const AttnLayout lay(p.cap, G);
+    unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + lay.bars);
+    unsigned short* ps = reinterpret_cast<unsigned short*>(smem + lay.ps);    // [8][kPsStride] probabilities, fp16
+    float* red = reinterpret_cast<float*>(smem + lay.red);                     // [warp][G][kPlaneStride] scores
+    float* alpha_s = reinterpret_cast<float*>(smem + lay.alpha);               // [8]
+    unsigned* koff = reinterpret_cast<unsigned*>(smem + lay.koff);             // [2][128] halves, relative to the block
+    unsigned* voff = reinterpret_cast<unsigned*>(smem + lay.voff);
+    int* kblk = reinterpret_cast<int*>(smem + lay.kblk);                       // block starts (uint32 units) of this split
+    int* vblk = reinterpret_cast<int*>(smem + lay.vblk);
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tb = lane >> 2, cp = lane & 3;   // fragment row (= bitmap byte) and k pair of this lane
+    const int h = blockIdx.y;
+    const int split = blockIdx.x + p.split_offset;
+    const bool is_window = split == p.nsplit;
+    unsigned sel, mh, ml;
+    lane_byte_constants(tb, sel, mh, ml);
+
+    // the compressed length may live in device memory (a captured launch keeps working while blocks are appended):
+    // p.nblk is then its upper bound, the grid was sized for that bound, and the blocks actually there are dealt
+    // out again over the same number of splits (splits past the end write an empty record)
+    int nblk = p.nblk, bps = p.bps;
+    if (p.L_dev) {
+        nblk = max(0, min(*p.L_dev / 64, p.nblk));
+        bps = p.nsplit > 0 ? (nblk + p.nsplit - 1) / p.nsplit : 0;
+    }
+    const int blk0 = is_window ? 0 : split * bps;
+    const int W = (is_window && p.W_dev) ? max(0, min(*p.W_dev, p.W)) : p.W;
+    int nb = is_window ? (W + 63) / 64 : min(bps, nblk - blk0);
+    if (nb < 0) nb = 0;
+
+    // ---- prologue
+    // q fragments (B operand of the K phase) of this warp's 32 channels: n = head tb, k pairs 2*cp, 2*cp+1 (+8)
+    unsigned qb[2][2] = {{0u, 0u}, {0u, 0u}};
+    if (tb < G) {
+        const __half* qrow = p.q + (static_cast<int64_t>(h) * G + tb) * p.q_stride + warp * 32 + 2 * cp;
+#pragma unroll
+        for (int kg = 0; kg < 2; ++kg)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) qb[kg][j] = ldg_nc_u32(qrow + kg * 16 + j * 8);
+    }
+    for (int i = tid; i < 8 * kPsStride / 2; i += kAThreads) reinterpret_cast<unsigned*>(ps)[i] = 0u;
+    const int* kacc = p.k.acc + h * p.k.acc_hs;
+    const int* vacc = p.v.acc + h * p.v.acc_hs;
+    if (!is_window) {
+        for (int i = tid; i <= nb; i += kAThreads) {
+            kblk[i] = kacc[static_cast<int64_t>(blk0 + i) * kTilesPerBlock];
+            vblk[i] = vacc[static_cast<int64_t>(blk0 + i) * kTilesPerBlock];
+        }
+    }
+    if (tid == 0) {
+        for (int s = 0; s < kAStages; ++s) mbar_init(&bars[s], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    const int64_t k_head0 = p.k.nz_off ? 8ll * p.k.nz_off[h] : h * p.k.nz_hs;
+    const int64_t v_head0 = p.v.nz_off ? 8ll * p.v.nz_off[h] : h * p.v.nz_hs;
+    const __half* knz = p.k.nz + k_head0;
+    const __half* vnz = p.v.nz + v_head0;
+    const size_t stg = attn_stage_bytes(p.cap);
+    const unsigned capb = static_cast<unsigned>(p.cap) * 2u;
+
+    // producer: bring block i of this split into stage i % kAStages (thread 0 only)
+    auto issue = [&](int i) {
+        unsigned char* st = smem + lay.stages + static_cast<size_t>(i % kAStages) * stg;
+        unsigned long long* bar = &bars[i % kAStages];
+        const int64_t tile0 = static_cast<int64_t>(blk0 + i) * kTilesPerBlock;
+        unsigned kbytes = static_cast<unsigned>(kblk[i + 1] - kblk[i]) * 4u;
+        unsigned vbytes = static_cast<unsigned>(vblk[i + 1] - vblk[i]) * 4u;
+        const bool bad = block_range_bad(kblk[i], kblk[i + 1], capb, k_head0, p.k.nz_extent) ||
+                         block_range_bad(vblk[i], vblk[i + 1], capb, v_head0, p.v.nz_extent);
+        if (bad) {   // the bitmaps are still copied, the values are not
+            if (p.dev_status) atomicOr(p.dev_status, MFAR_DEV_BADMETA);
+            kbytes = vbytes = 0;
+        }
+        mbar_expect_tx(bar, 2048 + kbytes + vbytes);
+        bulk_g2s(st + lay.s_kbm, p.k.bmp + h * p.k.bmp_hs + tile0, 1024, bar);
+        if (kbytes) bulk_g2s(st + lay.s_kval, knz + 2ll * kblk[i], kbytes, bar);
+        bulk_g2s(st + lay.s_vbm, p.v.bmp + h * p.v.bmp_hs + tile0, 1024, bar);
+        if (vbytes) bulk_g2s(st + lay.s_vval, vnz + 2ll * vblk[i], vbytes, bar);
+    };
+
+    // per-tile offsets of the next block travel through registers (one K and one V tile per thread)
+    int nxt_k = 0, nxt_v = 0;
+    auto fetch_offsets = [&](int i) {
+        const int64_t t = static_cast<int64_t>(blk0 + i) * kTilesPerBlock + tid;
+        nxt_k = kacc[t];
+        nxt_v = vacc[t];
+    };
+    auto store_offsets = [&](int i) {
+        const unsigned lim = static_cast<unsigned>(p.cap);
+        koff[(i & 1) * 128 + tid] = min(static_cast<unsigned>(2 * (nxt_k - kblk[i])), lim);
+        voff[(i & 1) * 128 + tid] = min(static_cast<unsigned>(2 * (nxt_v - vblk[i])), lim);
+    };
+
+    if (!is_window && nb > 0) {
+        if (tid == 0)
+            for (int i = 0; i < min(nb, kAStages - 1); ++i) issue(i);
+        fetch_offsets(0);
+        store_offsets(0);
+    }
+    __syncthreads();
+
+    // running state.  dv[hf][i]: rows = channels 64*hf + 8*tb + i (d0, d1) and + 4 (d2, d3); columns = heads 2*cp, 2*cp+1
+    float dv[2][4][4];
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dv[a][i][e] = 0.f;
+    // softmax state of head g lives in warp g % 4: m uniform, l a per-lane partial sum
+    constexpr int kHeadsPerWarp = (G + kAWarps - 1) / kAWarps;
+    float m_run[kHeadsPerWarp], l_run[kHeadsPerWarp];
+#pragma unroll
+    for (int j = 0; j < kHeadsPerWarp; ++j) { m_run[j] = -INFINITY; l_run[j] = 0.f; }
+
+    bool timed_out = false;
+    for (int i = 0; i < nb; ++i) {
+        const unsigned char* st = smem + lay.stages + static_cast<size_t>(i % kAStages) * stg;
+        const uint2* kbm = reinterpret_cast<const uint2*>(st + lay.s_kbm);
+        const uint2* vbm = reinterpret_cast<const uint2*>(st + lay.s_vbm);
+        const unsigned short* kval = reinterpret_cast<const unsigned short*>(st + lay.s_kval);
+        const unsigned short* vval = reinterpret_cast<const unsigned short*>(st + lay.s_vval);
+        const unsigned* ko = koff + (i & 1) * 128;
+        const unsigned* vo = voff + (i & 1) * 128;
+
+        if (!is_window) {
+            if (i + 1 < nb) fetch_offsets(i + 1);
+            if (!mbar_wait(&bars[i % kAStages], (i / kAStages) & 1)) timed_out = true;
+        }
+        if (__syncthreads_or(timed_out)) { timed_out = true; break; }   // also publishes the stage hand-off below
+        // every warp is done with block i-1, so its stage can take block i + kAStages - 1
+        if (!is_window && tid == 0 && i + kAStages - 1 < nb) issue(i + kAStages - 1);
+
+        // ------------------------------------------------------------ K phase: this warp's 32 channels x 64 tokens
+        // dk[j]: rows = tokens 8*tb + j (d0, d1) and 8*tb + j + 4 (d2, d3); columns = heads 2*cp, 2*cp+1
+        float dk[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) dk[j][e] = 0.f;
+        if (!is_window) {
+#pragma unroll
+            for (int kg = 0; kg < 2; ++kg) {
+                unsigned r1[8], r2[8];
+                {
+                    const int c = warp * 32 + kg * 16 + 2 * cp;
+                    const uint4 bm = *reinterpret_cast<const uint4*>(kbm + c);
+                    const uint2 of = *reinterpret_cast<const uint2*>(ko + c);
+                    expand_pair(bm, kval + of.x, kval + of.y, sel, mh, ml, r1);
+                }
+                {
+                    const int c = warp * 32 + kg * 16 + 8 + 2 * cp;
+                    const uint4 bm = *reinterpret_cast<const uint4*>(kbm + c);
+                    const uint2 of = *reinterpret_cast<const uint2*>(ko + c);
+                    expand_pair(bm, kval + of.x, kval + of.y, sel, mh, ml, r2);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma16816(dk[j], r1[j], r1[j + 4], r2[j], r2[j + 4], qb[kg][0], qb[kg][1]);
+            }
+        } else {
+            // dense window: the A fragment is two adjacent channels of one token, a 32-bit load
+            const __half* kw = p.kwin + h * p.win_hs;
+#pragma unroll
+            for (int kg = 0; kg < 2; ++kg) {
+                const int c = warp * 32 + kg * 16 + 2 * cp;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int t0 = i * 64 + 8 * tb + j, t1 = t0 + 4;
+                    unsigned a0 = 0, a1 = 0, a2 = 0, a3 = 0;
+                    if (t0 < W) { a0 = ldg_nc_u32(kw + t0 * p.win_ts + c); a2 = ldg_nc_u32(kw + t0 * p.win_ts + c + 8); }
+                    if (t1 < W) { a1 = ldg_nc_u32(kw + t1 * p.win_ts + c); a3 = ldg_nc_u32(kw + t1 * p.win_ts + c + 8); }
+                    mma16816(dk[j], a0, a1, a2, a3, qb[kg][0], qb[kg][1]);
+                }
+            }
+        }
+        // score planes [warp][head][slot], slot = 8*j + tb for token 8*tb + j (consecutive lanes, consecutive words)
+        {
+            float* pl = red + static_cast<size_t>(warp) * G * kPlaneStride;
+            if (2 * cp < G) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    pl[(2 * cp) * kPlaneStride + j * 8 + tb] = dk[j][0];
+                    pl[(2 * cp) * kPlaneStride + (j + 4) * 8 + tb] = dk[j][2];
+                }
+            }
+            if (2 * cp + 1 < G) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    pl[(2 * cp + 1) * kPlaneStride + j * 8 + tb] = dk[j][1];
+                    pl[(2 * cp + 1) * kPlaneStride + (j + 4) * 8 + tb] = dk[j][3];
+                }
+            }
+        }
+        __syncthreads();
+
+        // ------------------------------------------------------------ scores -> probabilities (warp g % 4 owns head g)
+#pragma unroll
+        for (int j = 0; j < kHeadsPerWarp; ++j) {
+            const int g = warp + j * kAWarps;
+            if (g < G) {
+                float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+                for (int w = 0; w < kAWarps; ++w) {
+                    const float2 t = *reinterpret_cast<const float2*>(red + (static_cast<size_t>(w) * G + g) * kPlaneStride + 2 * lane);
+                    s0 += t.x;
+                    s1 += t.y;
+                }
+                // slots 2*lane, 2*lane + 1 hold tokens 16*(lane % 4) + lane / 4 and + 8
+                const int tok0 = 16 * (lane & 3) + (lane >> 2), tok1 = tok0 + 8;
+                s0 *= p.scale_log2;
+                s1 *= p.scale_log2;
+                if (is_window) {
+                    if (i * 64 + tok0 >= W) s0 = -INFINITY;
+                    if (i * 64 + tok1 >= W) s1 = -INFINITY;
+                }
+                const float m_new = fmaxf(m_run[j], warp_max_f32(fmaxf(s0, s1)));
+                const float a = fast_exp2(m_run[j] - m_new);   // exp2(-inf) = 0 on the first block
+                // the probability that enters P.V is rounded to fp16 (as the reference model does before its
+                // value op); the running sum uses the same rounded value
+                const __half h0 = __float2half_rn(fast_exp2(s0 - m_new)), h1 = __float2half_rn(fast_exp2(s1 - m_new));
+                l_run[j] = l_run[j] * a + (__half2float(h0) + __half2float(h1));
+                m_run[j] = m_new;
+                ps[g * kPsStride + tok0] = __half_as_ushort(h0);
+                ps[g * kPsStride + tok1] = __half_as_ushort(h1);
+                if (lane == 0) alpha_s[g] = a;
+            }
+        }
+        if (!is_window && i + 1 < nb) store_offsets(i + 1);
+        __syncthreads();
+
+        // ------------------------------------------------------------ V phase: this warp's 16 tokens x 128 channels
+        {
+            float a0 = 1.f, a1 = 1.f;
+            if (2 * cp < G) a0 = alpha_s[2 * cp];
+            if (2 * cp + 1 < G) a1 = alpha_s[2 * cp + 1];
+            if (__any_sync(kFull, a0 != 1.f || a1 != 1.f)) {
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        dv[hf][j][0] *= a0; dv[hf][j][1] *= a1;
+                        dv[hf][j][2] *= a0; dv[hf][j][3] *= a1;
+                    }
+            }
+        }
+        // probabilities as the B operand: n = head tb, k pairs = tokens 16*warp + 2*cp, +1 (+8)
+        const unsigned pb0 = *reinterpret_cast<const unsigned*>(ps + tb * kPsStride + warp * 16 + 2 * cp);
+        const unsigned pb1 = *reinterpret_cast<const unsigned*>(ps + tb * kPsStride + warp * 16 + 8 + 2 * cp);
+        if (!is_window) {
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                unsigned r1[8], r2[8];
+                {
+                    const int t = hf * 64 + warp * 16 + 2 * cp;
+                    const uint4 bm = *reinterpret_cast<const uint4*>(vbm + t);
+                    const uint2 of = *reinterpret_cast<const uint2*>(vo + t);
+                    expand_pair(bm, vval + of.x, vval + of.y, sel, mh, ml, r1);
+                }
+                {
+                    const int t = hf * 64 + warp * 16 + 8 + 2 * cp;
+                    const uint4 bm = *reinterpret_cast<const uint4*>(vbm + t);
+                    const uint2 of = *reinterpret_cast<const uint2*>(vo + t);
+                    expand_pair(bm, vval + of.x, vval + of.y, sel, mh, ml, r2);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma16816(dv[hf][j], r1[j], r1[j + 4], r2[j], r2[j + 4], pb0, pb1);
+            }
+        } else {
+            // dense window: the A fragment pairs two adjacent tokens of one channel (two 16-bit loads)
+            const __half* vw = p.vwin + h * p.win_hs;
+            const int tA = i * 64 + warp * 16 + 2 * cp;
+            auto pair = [&](int t, int ch) -> unsigned {
+                unsigned lo = 0, hi = 0;
+                if (t < W) lo = ldg_nc_u16(vw + t * p.win_ts + ch);
+                if (t + 1 < W) hi = ldg_nc_u16(vw + (t + 1) * p.win_ts + ch);
+                return __byte_perm(lo, hi, 0x5410);
+            };
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c0 = hf * 64 + 8 * tb + j, c1 = c0 + 4;
+                    mma16816(dv[hf][j], pair(tA, c0), pair(tA, c1), pair(tA + 8, c0), pair(tA + 8, c1), pb0, pb1);
+                }
+        }
+    }
+
+    if (timed_out && tid == 0 && p.dev_status) atomicOr(p.dev_status, MFAR_DEV_TIMEOUT);
+
+    // ---- epilogue: sum the four warps' partial outputs and write the record (an empty one after a timeout, so
+    // that the merge below still sees every record arrive)
+    __syncthreads();
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c0 = hf * 64 + 8 * tb + j, c1 = c0 + 4;
+            if (2 * cp < G) {
+                red[(static_cast<size_t>(warp) * G + 2 * cp) * kD + c0] = dv[hf][j][0];
+                red[(static_cast<size_t>(warp) * G + 2 * cp) * kD + c1] = dv[hf][j][2];
+            }
+            if (2 * cp + 1 < G) {
+                red[(static_cast<size_t>(warp) * G + 2 * cp + 1) * kD + c0] = dv[hf][j][1];
+                red[(static_cast<size_t>(warp) * G + 2 * cp + 1) * kD + c1] = dv[hf][j][3];
+            }
+        }
+    __syncthreads();
+    for (int idx = tid; idx < G * kD; idx += kAThreads) {
+        const int g = idx / kD, c = idx % kD;
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < kAWarps; ++w) s += red[(static_cast<size_t>(w) * G + g) * kD + c];
+        record_ptr(p, G, h, split, g)[c] = timed_out ? 0.f : s;
+    }
+#pragma unroll
+    for (int j = 0; j < kHeadsPerWarp; ++j) {
+        const int g = warp + j * kAWarps;
+        if (g < G) {
+            const float l = warp_sum_f32(l_run[j]);
+            if (lane == 0) {
+                float* rec = record_ptr(p, G, h, split, g);
+                rec[kPartM] = timed_out ? -INFINITY : m_run[j];
+                rec[kPartL] = timed_out ? 0.f : l;
+            }
+        }
+    }
+
+    // ---- merge: the CTA that arrives last at this kv head's counter combines all records
+    //      out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+    if (p.counters == nullptr) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned arrived = atomicAdd(p.counters + h, 1u) + 1u;
+        s_last = arrived == gridDim.x;
+        if (s_last) p.counters[h] = 0u;   // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const int nrec = p.nrec;
+    for (int g = 0; g < G; ++g) {
+        const float* base = record_ptr(p, G, h, 0, g);
+        const int64_t step = static_cast<int64_t>(p.rec_group) * kPartialStride;
+        float M = -INFINITY;
+        for (int s = 0; s < nrec; ++s) M = fmaxf(M, ldcg_f32(base + s * step + kPartM));
+        float o = 0.f, l = 0.f;
+        int s = 0;
+        for (; s + 4 <= nrec; s += 4) {
+            float ms[4], ls[4], vs[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                ms[u] = ldcg_f32(base + (s + u) * step + kPartM);
+                ls[u] = ldcg_f32(base + (s + u) * step + kPartL);
+                vs[u] = ldcg_f32(base + (s + u) * step + tid);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float w = (ms[u] == -INFINITY) ? 0.f : fast_exp2(ms[u] - M);
+                l += w * ls[u];
+                o += w * vs[u];
+            }
+        }
+        for (; s < nrec; ++s) {
+            const float m1 = ldcg_f32(base + s * step + kPartM);
+            const float w = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - M);
+            l += w * ldcg_f32(base + s * step + kPartL);
+            o += w * ldcg_f32(base + s * step + tid);
+        }
+        p.out[(static_cast<int64_t>(h) * G + g) * p.out_stride + tid] = __float2half_rn(l > 0.f ? o / l : 0.f);
+    }
+}
+
+template <int G>
+static int launch_attn(const DecodeParams& p, int n_kv_heads, int grid_x, cudaStream_t s) {
+    const AttnLayout lay(p.cap, G);
+    static size_t configured[64] = {0};   // largest dynamic shared memory size opted into so far, per device
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MFAR_ERR_LAUNCH;
+    if (lay.total > configured[dev]) {
+        if (cudaFuncSetAttribute(decode_attn_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(lay.total)) != cudaSuccess)
+            return MFAR_ERR_LAUNCH;
+        configured[dev] = lay.total;
+    }
+    decode_attn_kernel<G><<<dim3(grid_x, n_kv_heads), kAThreads, lay.total, s>>>(p);
+    return launch_status();
+}
+
+int launch_decode_attn(const DecodeParams& p, int G, int n_kv_heads, int grid_x, cudaStream_t s) {
+    switch (G) {
+        case 1: return launch_attn<1>(p, n_kv_heads, grid_x, s);
+        case 2: return launch_attn<2>(p, n_kv_heads, grid_x, s);
+        case 4: return launch_attn<4>(p, n_kv_heads, grid_x, s);
+        case 8: return launch_attn<8>(p, n_kv_heads, grid_x, s);
+        default: return MFAR_ERR_ARG;
+    }
+}
+
+int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G, const void* kwin, const void* vwin,
+                         int64_t win_hs, int64_t win_ts, int W, const int* W_dev, float softmax_scale, float* ws,
+                         int rec_index, unsigned* dev_status, cudaStream_t s, bool halves8) {
+    if (!kwin || !vwin || !q) return MFAR_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(kwin) & 15) || (reinterpret_cast<uintptr_t>(vwin) & 15) || (win_hs & 7) ||
+        (win_ts & 7) || (reinterpret_cast<uintptr_t>(q) & 3) || (q_stride & 1))
+        return MFAR_ERR_ALIGN;
+    DecodeParams p{};
+    p.q = static_cast<const __half*>(q);
+    p.q_stride = q_stride;
+    p.kwin = static_cast<const __half*>(kwin);
+    p.vwin = static_cast<const __half*>(vwin);
+    p.win_hs = win_hs;
+    p.win_ts = win_ts;
+    p.W = W;
+    p.W_dev = W_dev;
+    p.nsplit = rec_index;
+    p.split_offset = rec_index;
+    p.nrec = rec_index + 1;
+    p.rec_group = (halves8 && G == 8) ? 4 : G;
+    p.cap = 8;
+    p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    p.ws = ws;
+    p.dev_status = dev_status;
+    return launch_decode_attn(p, G, n_kv_heads, 1, s);
+}
+
+}  // namespace mfar

@@ -1,6 +1,6 @@
 // Building blocks shared by the fp16 and the quantised decode kernels:
-// mbarrier / bulk-copy wrappers (1-D cp.async.bulk, no multicast), the split-KV
-// partial record, and the combine kernel.
+// mbarrier / bulk-copy wrappers (1-D cp.async.bulk, no multicast), the position-centric
+// tile step, the split-KV partial record and the launch parameters.
 #pragma once
 
 #include "common.cuh"
@@ -73,36 +73,36 @@ __device__ __forceinline__ float warp_sum_f32(float v) {
 // multiply-accumulated in fp32 into acc[i][g] with the per-tile coefficients coef[g]
 // (K phase: the query channel; V phase: the probability of the token).  The compiler turns
 // the `if` into predicated instructions (no branch, no zero fill).
-#ifndef MFAR_CHAINS
-#define MFAR_CHAINS 2
-#endif
-template <int G>
-__device__ __forceinline__ void tile_step(unsigned hi, unsigned lo, const unsigned short* vals, unsigned sel,
-                                          unsigned mh, unsigned ml, const float (&coef)[G], float (&acc)[8][G]) {
-    const unsigned byte = __byte_perm(lo, hi, sel);
-    // MFAR_CHAINS independent read pointers (each covers 8 / MFAR_CHAINS positions) keep the
-    // dependent chain of pointer bumps short
-    const unsigned short* pv[MFAR_CHAINS];
-    pv[0] = vals + (__popc(hi & mh) + __popc(lo & ml));
-#pragma unroll
-    for (int c = 1; c < MFAR_CHAINS; ++c)
-        pv[c] = pv[0] + __popc(byte & (0xffu & ~(0xffu >> (c * (8 / MFAR_CHAINS)))));
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const unsigned short*& p = pv[i / (8 / MFAR_CHAINS)];
-        if (byte & (0x80u >> i)) {
-            const float v = __half2float(__ushort_as_half(*p));
-            ++p;
-#pragma unroll
-            for (int g = 0; g < G; ++g) acc[i][g] = fmaf(v, coef[g], acc[i][g]);
-        }
-    }
-}
-
 __device__ __forceinline__ void lane_byte_constants(int kb, unsigned& sel, unsigned& mh, unsigned& ml) {
     sel = 7u - kb;
     mh = kb == 0 ? 0u : (kb >= 4 ? 0xffffffffu : (0xffffffffu << (32 - 8 * kb)));
     ml = kb <= 4 ? 0u : (0xffffffffu << (64 - 8 * kb));
+}
+
+__device__ __forceinline__ float fma_h(float acc, unsigned short a, unsigned short b) {
+    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc) : "h"(a), "h"(b));
+    return acc;
+}
+
+// The packed half and the fp16 coefficient go straight into one mixed-precision FMA (fp16 x fp16 + fp32, full rate
+// on sm_100).  Two read pointers (positions 0-3 and 4-7) keep the dependent chain of pointer bumps short.
+template <int G>
+__device__ __forceinline__ void tile_step(unsigned hi, unsigned lo, const unsigned short* vals, unsigned sel,
+                                          unsigned mh, unsigned ml, const unsigned short (&coef)[G], float (&acc)[8][G]) {
+    const unsigned byte = __byte_perm(lo, hi, sel);
+    const unsigned short* pv[2];
+    pv[0] = vals + (__popc(hi & mh) + __popc(lo & ml));
+    pv[1] = pv[0] + __popc(byte & 0xf0u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        if (byte & (0x80u >> i)) {
+            const unsigned short*& p = pv[i / 4];
+            const unsigned short v = *p;
+            ++p;
+#pragma unroll
+            for (int g = 0; g < G; ++g) acc[i][g] = fma_h(acc[i][g], v, coef[g]);
+        }
+    }
 }
 
 template <int G>
@@ -119,48 +119,6 @@ __device__ __forceinline__ void load_coef(const float* p, float (&c)[G]) {
             c[g] = t.x; c[g + 1] = t.y; c[g + 2] = t.z; c[g + 3] = t.w;
         }
     }
-}
-
-__device__ __forceinline__ float fma_h(float acc, unsigned short a, unsigned short b) {
-    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc) : "h"(a), "h"(b));
-    return acc;
-}
-
-// fp16-coefficient tile step: the packed half and the coefficient go straight into one mixed-precision
-// FMA (fp16 x fp16 + fp32, full rate on sm_100), which saves the fp16 -> fp32 conversion of every value.
-template <int G>
-__device__ __forceinline__ void tile_step(unsigned hi, unsigned lo, const unsigned short* vals, unsigned sel,
-                                          unsigned mh, unsigned ml, const unsigned short (&coef)[G], float (&acc)[8][G]) {
-    const unsigned byte = __byte_perm(lo, hi, sel);
-#if MFAR_CHAINS >= 2
-    // MFAR_CHAINS read pointers (8 / MFAR_CHAINS positions each) shorten the dependent chain of pointer bumps
-    const unsigned short* pv[MFAR_CHAINS];
-    pv[0] = vals + (__popc(hi & mh) + __popc(lo & ml));
-#pragma unroll
-    for (int c = 1; c < MFAR_CHAINS; ++c)
-        pv[c] = pv[0] + __popc(byte & (0xffu & ~(0xffu >> (c * (8 / MFAR_CHAINS)))));
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        if (byte & (0x80u >> i)) {
-            const unsigned short*& p = pv[i / (8 / MFAR_CHAINS)];
-            const unsigned short v = *p;
-            ++p;
-#pragma unroll
-            for (int g = 0; g < G; ++g) acc[i][g] = fma_h(acc[i][g], v, coef[g]);
-        }
-    }
-#else
-    const unsigned short* pv = vals + (__popc(hi & mh) + __popc(lo & ml));
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        if (byte & (0x80u >> i)) {
-            const unsigned short v = *pv;
-            ++pv;
-#pragma unroll
-            for (int g = 0; g < G; ++g) acc[i][g] = fma_h(acc[i][g], v, coef[g]);
-        }
-    }
-#endif
 }
 
 template <int G>
@@ -197,6 +155,7 @@ constexpr int kPartL = kD + 1;
 
 enum { MODE_ATTN = 0, MODE_KEY = 1, MODE_VALUE = 2 };
 constexpr int kSlackHalves = 64;  // a decode never reads further than this past a stage's values
+constexpr int kMaxBlocksPerSplit = 256;
 
 struct Sparse {
     const unsigned long long* bmp;
@@ -204,6 +163,7 @@ struct Sparse {
     const __half* nz;
     const int* nz_off;
     int64_t bmp_hs, acc_hs, nz_hs;
+    int64_t nz_extent;   // halves addressable from nz (0 = unknown: the extent check is skipped)
 };
 
 struct DecodeParams {
@@ -216,32 +176,51 @@ struct DecodeParams {
     int W;
     const int* W_dev;      // optional: window length in device memory (then W is its upper bound)
     const int* L_dev;      // optional: compressed tokens in device memory (then nblk is their upper bound, in blocks)
-    int kv_share;          // grid rows (groups of query heads) that share one kv head; 0 is read as 1
     int nblk, nsplit, bps; // compressed blocks, splits over them, blocks per split
     int cap;               // halves of packed values a stage can hold per tensor
     float scale_log2;      // softmax scale * log2(e)
     float* ws;             // split partials
+    int nrec;              // partial records per kv head in ws
+    int rec_group;         // query heads per record set: G, or 4 when 8 heads are laid out as two sets of 4
     __half* s_out;         // MODE_KEY  : [Bq][s_stride]
     int64_t s_stride;
     const __half* p_in;    // MODE_VALUE: [Bq][p_stride]
     int64_t p_stride;
     unsigned* dev_status;
     int split_offset;      // added to blockIdx.x (lets a launch cover only the window record)
+    int kv_share;          // single-product kernels: grid rows (sets of query heads) sharing one kv head; 0 reads as 1
+    // fused attention only: the CTA that finishes a kv head last merges its records into out
+    unsigned* counters;    // one per kv head, zero between launches; NULL = no merge (a combine launch follows)
+    __half* out;
+    int64_t out_stride;
 };
 
+// The first kCounterBytes of every decode workspace hold one arrival counter per kv head (fused attention); the
+// split records of every entry point start behind them, whatever the head count, so that calls of different shapes
+// can share a workspace without touching each other's counters.
+constexpr size_t kCounterBytes = 64 * 1024;
+constexpr int kMaxCountedHeads = static_cast<int>(kCounterBytes / 4);
+inline size_t counters_bytes(int) { return kCounterBytes; }
 
-// 64-token-block kernel (decode.cu) and 256-token-superblock kernel (decode_sb.cu)
-int launch_decode_sb(const DecodeParams& p, int G, int n_kv_heads, cudaStream_t s);
-bool decode_sb_fits(int cap, int G);
-// barrier-free 64-token-block kernel (decode_stream.cu); mixed = fp16 coefficients, one mixed-precision FMA per head
-int launch_decode_stream(const DecodeParams& p, int G, int n_kv_heads, bool mixed, cudaStream_t s);
-int decode_stream_max_blocks();
+// Checks one 64-token block's packed range before it is copied: block start `blk` and end `nxt` in uint32 units
+// (entries of accum), stage capacity `capb` in bytes, start of the head inside nz and the extent of nz in halves.
+// A bulk copy needs a 16-byte aligned source and a size that is a multiple of 16 bytes.
+__device__ __forceinline__ bool block_range_bad(int blk, int nxt, unsigned capb, int64_t head_start_halves,
+                                                int64_t nz_extent) {
+    const long long d = (static_cast<long long>(nxt) - blk) * 4;
+    bool bad = d < 0 || d > capb || blk < 0 || (blk & 3) || (d & 15);
+    if (nz_extent > 0) bad |= head_start_halves + 2ll * nxt > nz_extent;
+    return bad;
+}
+
+// fused decode attention (decode_attn.cu): grid (grid_x, n_kv_heads); G in {1, 2, 4, 8}
+int launch_decode_attn(const DecodeParams& p, int G, int n_kv_heads, int grid_x, cudaStream_t s);
 // merge of the split-KV records (normalise = 1) or plain sum (normalise = 0), one CTA per q head
 int launch_combine(const float* ws, int nrec, int G, int normalise, void* out, int64_t out_stride, int n_q_heads,
                    cudaStream_t s);
 // dense recent-token window as split record `rec_index` of a workspace with rec_index + 1 records per kv head.
-// halves8: with G = 8 the records are laid out as two groups of 4 query heads per kv head
-// ([kv head * 2 + half][record][4], what the block kernels write) instead of [kv head][record][8]
+// halves8: with G = 8 the records are laid out as two sets of 4 query heads per kv head
+// ([kv head * 2 + half][record][4]) instead of [kv head][record][8]
 int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G, const void* kwin, const void* vwin,
                          int64_t win_hs, int64_t win_ts, int W, const int* W_dev, float softmax_scale, float* ws,
                          int rec_index, unsigned* dev_status, cudaStream_t s, bool halves8 = false);
@@ -250,21 +229,22 @@ int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G,
 // The cost of a candidate follows a model fitted to a measured sweep of ns over batch 1..64 and
 // 4k..32k tokens on a B200 (all times in units of one block on an otherwise idle SM, ~2 us):
 //   * a CTA costs w = bps + 1.1 (prologue, partial record);
-//   * x = CTAs / 148 is the load per SM; an SM's throughput with o = min(x, 4) resident CTAs is
+//   * x = CTAs / SMs is the load per SM; an SM's throughput with o = min(x, 4) resident CTAs is
 //     rate(o) = 1 / 2 / 2.76 / 2.13 at o = 1 / 2 / 3 / 4, linear in between (the dip at 4 is the fit's
 //     way of saying that a grid which fits in one not-quite-full wave beats one that needs two);
 //   * the last, partly filled wave costs another 0.8 w once the SMs hold more than one CTA;
-//   * the combine kernel adds 0.035 per record.
+//   * merging the records adds 0.035 per record.
 // The pick stays within 2 % of the best swept ns on every measured shape.
-inline int model_split_count(int n_kv_heads, int nblk, int min_ns, int max_ns) {
+inline int model_split_count(int n_kv_heads, int nblk, int min_ns, int max_ns, int n_sm) {
     if (max_ns > nblk) max_ns = nblk;
     if (min_ns < 1) min_ns = 1;
+    if (n_sm < 1) n_sm = 1;
     int ns = min_ns;
     double best = -1.0;
     for (int cand = min_ns; cand <= max_ns; ++cand) {
         const int bps = (nblk + cand - 1) / cand;
         const int real = (nblk + bps - 1) / bps;
-        const double x = static_cast<double>(n_kv_heads) * real / 148.0;
+        const double x = static_cast<double>(n_kv_heads) * real / n_sm;
         const double w = bps + 1.1;
         double cost = w;
         if (x > 1.0) {

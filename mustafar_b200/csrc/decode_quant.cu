@@ -409,7 +409,7 @@ static int check_q(const void* bmp, const void* off, const void* sc, const void*
 
 static void q_split(int n_kv_heads, int nblk, int hint, int* ns, int* bps) {
     const int max_n = (nblk + 1) / 2;   // what callers size their workspace for
-    int n = hint > 0 ? hint : model_split_count(n_kv_heads, nblk, 1, max_n < 128 ? max_n : 128);
+    int n = hint > 0 ? hint : model_split_count(n_kv_heads, nblk, 1, max_n < 128 ? max_n : 128, device_sm_count());
     if (n > nblk) n = nblk;
     if (n < 1) n = 1;
     *bps = (nblk + n - 1) / n;
@@ -464,12 +464,12 @@ extern "C" int mfar_value_output_quant(const void* probs, int64_t probs_stride, 
     p.nblk = n_tokens / 64;
     q_split(n_kv_heads, p.nblk, nsplit, &p.nsplit, &p.bps);
     p.nrec = p.nsplit;
-    const size_t need = static_cast<size_t>(n_kv_heads) * p.nrec * group * kPartialStride * sizeof(float);
+    const size_t need = counters_bytes(n_kv_heads) + static_cast<size_t>(n_kv_heads) * p.nrec * group * kPartialStride * sizeof(float);
     if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)) return MFAR_ERR_WORKSPACE;
     p.group32 = qgroup == 32;
     p.p_in = static_cast<const __half*>(probs);
     p.p_stride = probs_stride;
-    p.ws = static_cast<float*>(workspace);
+    p.ws = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + counters_bytes(n_kv_heads));
     p.dev_status = dev_status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     r = dispatch_q<MODE_VALUE>(p, group, bits, n_kv_heads, s);
@@ -502,9 +502,9 @@ extern "C" int mfar_decode_attention_quant(
         q_split(n_kv_heads, p.nblk, nsplit, &p.nsplit, &p.bps);
     }
     p.nrec = p.nsplit + (window > 0 ? 1 : 0);
-    const size_t need = static_cast<size_t>(n_kv_heads) * p.nrec * group * kPartialStride * sizeof(float);
+    const size_t need = counters_bytes(n_kv_heads) + static_cast<size_t>(n_kv_heads) * p.nrec * group * kPartialStride * sizeof(float);
     if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)) return MFAR_ERR_WORKSPACE;
-    p.ws = static_cast<float*>(workspace);
+    p.ws = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + counters_bytes(n_kv_heads));
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.dev_status = dev_status;
     if (n_tokens > 0) {

@@ -70,12 +70,17 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__half* x, const __hal
 __global__ void __launch_bounds__(64) rope_append_kernel(const __half* qkv, const float* inv_freq, const int* pos_dev,
                                                          int pos_host, const int* widx_dev, int widx_host, int hq, int hkv,
                                                          __half* q_out, __half* kwin, __half* vwin, int64_t win_hs,
-                                                         int64_t win_ts) {
+                                                         int64_t win_ts, int capacity, unsigned* dev_status) {
     const int heads = hq + 2 * hkv;
     const int b = blockIdx.x / heads, hd = blockIdx.x % heads, i = threadIdx.x;
     const __half* src = qkv + (static_cast<int64_t>(b) * heads + hd) * kD;
     const __half x1 = src[i], x2 = src[i + 64];
     const int widx = widx_dev ? *widx_dev : widx_host;
+    // a slot outside the window (host and device counters out of step) is reported, never written
+    if (hd >= hq && (widx < 0 || widx >= capacity)) {
+        if (i == 0 && dev_status) atomicOr(dev_status, MFAR_DEV_BADMETA);
+        return;
+    }
     if (hd >= hq + hkv) {
         __half* dst = vwin + (static_cast<int64_t>(b) * hkv + (hd - hq - hkv)) * win_hs + widx * win_ts;
         dst[i] = x1;
@@ -130,8 +135,9 @@ extern "C" int mfar_add_rmsnorm_f16(void* x, const void* delta, const void* weig
 extern "C" int mfar_rope_append_f16(const void* qkv, const float* inv_freq, const int32_t* pos_dev, int pos,
                                     const int32_t* slot_dev, int slot, int batch, int n_q_heads, int n_kv_heads,
                                     void* q_out, void* k_window, void* v_window, int64_t win_head_stride,
-                                    int64_t win_token_stride, void* stream) {
-    if (batch < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || pos < 0 || slot < 0) return MFAR_ERR_ARG;
+                                    int64_t win_token_stride, int window_capacity, uint32_t* dev_status, void* stream) {
+    if (batch < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || pos < 0 || slot < 0 || window_capacity <= 0) return MFAR_ERR_ARG;
+    if (!slot_dev && slot >= window_capacity) return MFAR_ERR_ARG;
     if (batch == 0) return MFAR_OK;
     if (!qkv || !inv_freq || !q_out || !k_window || !v_window) return MFAR_ERR_ARG;
     const int64_t ctas = static_cast<int64_t>(batch) * (n_q_heads + 2 * n_kv_heads);
@@ -139,7 +145,7 @@ extern "C" int mfar_rope_append_f16(const void* qkv, const float* inv_freq, cons
     rope_append_kernel<<<static_cast<unsigned>(ctas), 64, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(qkv), inv_freq, pos_dev, pos, slot_dev, slot, n_q_heads, n_kv_heads,
         static_cast<__half*>(q_out), static_cast<__half*>(k_window), static_cast<__half*>(v_window), win_head_stride,
-        win_token_stride);
+        win_token_stride, window_capacity, dev_status);
     return launch_status();
 }
 
@@ -150,7 +156,8 @@ extern "C" int mfar_silu_mul_f16(const void* gate_up, void* out, int64_t rows, i
     if ((reinterpret_cast<uintptr_t>(gate_up) & 3) || (reinterpret_cast<uintptr_t>(out) & 3)) return MFAR_ERR_ALIGN;
     const int64_t n2 = rows * (width / 2);
     int64_t blocks = (n2 + 255) / 256;
-    if (blocks > 148 * 8) blocks = 148 * 8;
+    const int64_t sms = device_sm_count();
+    if (blocks > sms * 8) blocks = sms * 8;
     silu_mul_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __half*>(gate_up), static_cast<__half*>(out), rows, width);
     return launch_status();

@@ -74,7 +74,7 @@ def store_bytes(st):
 
 
 def bench_compress(quick):
-    Bh, L = (16, 4096) if quick else (64, 8192)              # BASELINE config 2: [8 x 8 heads, 8192 tokens, 128]
+    Bh, L = (16, 4096) if quick else (64, 8192)              # prefill shape [8 sequences x 8 kv heads, 8192 tokens, 128]
     for s in (0.5, 0.7):
         for kind, name in ((comp.KEY, "K"), (comp.VALUE, "V")):
             x = synth(Bh, L, 11, kind == comp.KEY)
@@ -170,11 +170,12 @@ def bench_decode(quick):
         out = torch.empty_like(q)
         hint = max(ks.stage_hint(), vs.stage_hint())
         nbytes = store_bytes(ks) + store_bytes(vs) + 2 * 2 * Bh * 128 * D + 4 * B * HQ * D
-        for variant in ("block", "stream16"):
-            us = timed(lambda: ops.decode_attention(q, ks, vs, kw, vw, G, out=out, stage_halves=hint, variant=variant))
-            emit(f"fused decode attention ({variant})", us, nbytes, batch=B, kv_len=L, window=128, sparsity=0.7)
-        us = timed_graph(lambda: ops.decode_attention(q, ks, vs, kw, vw, G, out=out, stage_halves=hint, variant="block"))
-        emit("fused decode attention (block, CUDA-graph replay)", us, nbytes, batch=B, kv_len=L, window=128, sparsity=0.7)
+        _, ws_bytes = ops.plan(Bh, L, 128, G)
+        ws = ops.new_workspace(q.device, ws_bytes)
+        us = timed(lambda: ops.decode_attention(q, ks, vs, kw, vw, G, out=out, stage_halves=hint, workspace=ws))
+        emit("fused decode attention", us, nbytes, batch=B, kv_len=L, window=128, sparsity=0.7)
+        us = timed_graph(lambda: ops.decode_attention(q, ks, vs, kw, vw, G, out=out, stage_halves=hint, workspace=ws))
+        emit("fused decode attention (CUDA-graph replay)", us, nbytes, batch=B, kv_len=L, window=128, sparsity=0.7)
         ops.check_device_status()
         del ks, vs
 
@@ -191,8 +192,10 @@ def bench_decode_groups(quick):
         q = synth(Bh * group, 1, 3, False).view(Bh * group, D)
         out = torch.empty_like(q)
         nbytes = store_bytes(ks) + store_bytes(vs) + 2 * 2 * Bh * 128 * D + 4 * Bh * group * D
-        us = timed_graph(lambda: ops.decode_attention(q, ks, vs, kw, vw, group, out=out, stage_halves=hint))
-        emit("fused decode attention (block, CUDA-graph replay)", us, nbytes, batch=B, kv_len=L, window=128, sparsity=0.7,
+        _, ws_bytes = ops.plan(Bh, L, 128, group)
+        ws = ops.new_workspace(q.device, ws_bytes)
+        us = timed_graph(lambda: ops.decode_attention(q, ks, vs, kw, vw, group, out=out, stage_halves=hint, workspace=ws))
+        emit("fused decode attention (CUDA-graph replay)", us, nbytes, batch=B, kv_len=L, window=128, sparsity=0.7,
              q_heads_per_kv_head=group)
     ops.check_device_status()
 

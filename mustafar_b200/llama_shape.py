@@ -139,6 +139,12 @@ class SparseLlama:
         # values of 64 tokens, a few ties, and the worst padding of its 128 tiles
         kept = D - self.rank_keep + 1
         self._stage_bound = min(8192, 64 * (kept + 3) + 7 * 128)
+        # the decode calls of this model write their split records here: a buffer of its own, sized for the full
+        # cache, so that captured graphs never see it move and other users of the ops cannot grow it away
+        self._decode_ws = None
+        if self.sparse and not self.quant:
+            _, nbytes = ops.plan(batch * self.hkv, self.max_tokens, self.wcap, self.G)
+            self._decode_ws = ops.new_workspace(self.dev, nbytes)
 
     # ------------------------------------------------------------------ pieces
     def _allreduce(self, x):
@@ -248,7 +254,8 @@ class SparseLlama:
                 step_ops.rope_append(qkv, self._inv_freq, self._state[0:1], self._state[1:2], self.hq, self.hkv,
                                      self._qbuf, L.kwin, L.vwin)
                 att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin, L.vwin, self.G, stage_halves=self._stage_bound,
-                                           window_len=self._state[2:3], n_tokens=self._state[3:4])
+                                           window_len=self._state[2:3], n_tokens=self._state[3:4],
+                                           workspace=self._decode_ws)
             elif self.quant:
                 step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin)
                 att = ops_quant.decode_attention_quant(self._qbuf, L.ks.as_dict(), L.vs.as_dict(), self.compressed,
@@ -256,7 +263,7 @@ class SparseLlama:
             else:
                 step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin)
                 att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G,
-                                           stage_halves=hint)
+                                           stage_halves=hint, workspace=self._decode_ws)
             o = F.linear(att.view(B, self.hq * D), L.wo)
             if tp:
                 yield o

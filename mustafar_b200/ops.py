@@ -27,11 +27,25 @@ def _debug_check() -> bool:
     return os.environ.get("MUSTAFAR_B200_CHECK", "0") == "1" and not torch.cuda.is_current_stream_capturing()
 
 
+def new_workspace(device, nbytes: int) -> torch.Tensor:
+    """A decode workspace of at least ``nbytes`` (see ``plan``).  Zero-filled: its first bytes are the arrival
+    counters of the fused attention kernel, which every call leaves at zero again."""
+    return torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+
+
 def _workspace(device, nbytes: int) -> torch.Tensor:
-    ws = _workspaces.get(device)
+    """Default workspace: one per (device, stream), grown on demand.  A caller that captures CUDA graphs or runs
+    decode calls on several streams hands its own buffer to ``decode_attention(workspace=...)`` instead: growing
+    this one while a captured graph still holds the old pointer would leave the graph writing into freed memory,
+    so growth during capture is refused."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspaces[device] = ws
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("decode workspace would have to grow during CUDA graph capture: pass workspace= "
+                               "(ops.new_workspace sized by ops.plan) to the captured calls")
+        ws = new_workspace(device, nbytes)
+        _workspaces[key] = ws
     return ws
 
 
@@ -50,7 +64,19 @@ def check_device_status(device=None) -> None:
             word = int(st.item())
             if word:
                 st.zero_()
+                for (d, _), ws in _workspaces.items():   # a kernel that gave up may have left counters behind
+                    if d == dev:
+                        ws.zero_()
             _lib.check_dev_status(word, "decode")
+
+
+def _take_workspace(workspace, device, nbytes: int) -> torch.Tensor:
+    if workspace is None:
+        return _workspace(device, nbytes)
+    if (not workspace.is_cuda or workspace.dtype != torch.uint8 or workspace.numel() < nbytes
+            or workspace.data_ptr() % 16 or not workspace.is_contiguous()):
+        raise RuntimeError(f"workspace must be a contiguous CUDA uint8 tensor of at least {nbytes} bytes, 16-byte aligned")
+    return workspace
 
 
 def plan(n_kv_heads: int, n_tokens: int, window: int, group: int, nsplit: int = 0):
@@ -98,7 +124,7 @@ def mustafar_key_formulation(bmp, NZ, idx, NZ_Offset, B, M_Global, K_Global, Bat
     rows = B.shape[1] if B.dim() == 3 else 1
     r = _lib.lib().mfar_key_scores_fp16(
         B.data_ptr(), rows * K_Global, n_kv, num_key_value_groups,
-        bmp.data_ptr(), tiles, idx.data_ptr(), tiles + 1, NZ.data_ptr(), NZ_Offset.data_ptr(), 0,
+        bmp.data_ptr(), tiles, idx.data_ptr(), tiles + 1, NZ.data_ptr(), NZ_Offset.data_ptr(), 0, NZ.numel(),
         M_Global, out.data_ptr(), 8 * M_Global, 0, st.data_ptr(), _stream())
     _lib.check(r, "mfar_key_scores_fp16")
     if _debug_check():
@@ -127,7 +153,7 @@ def mustafar_value_formulation(bmp, NZ, idx, NZ_Offset, B, Reduction_Workspace, 
     rows = Bc.shape[1] if Bc.dim() == 3 else 1
     r = _lib.lib().mfar_value_output_fp16(
         Bc.data_ptr(), rows * K_Global, n_kv, num_key_value_groups,
-        bmp.data_ptr(), tiles, idx.data_ptr(), tiles + 1, NZ.data_ptr(), NZ_Offset.data_ptr(), 0,
+        bmp.data_ptr(), tiles, idx.data_ptr(), tiles + 1, NZ.data_ptr(), NZ_Offset.data_ptr(), 0, NZ.numel(),
         K_Global, out.data_ptr(), 8 * M_Global, ws.data_ptr(), ws.numel(), 0, 0, st.data_ptr(), _stream())
     _lib.check(r, "mfar_value_output_fp16")
     if _debug_check():
@@ -138,26 +164,27 @@ def mustafar_value_formulation(bmp, NZ, idx, NZ_Offset, B, Reduction_Workspace, 
 def decode_attention(q: torch.Tensor, k_store: SparseStore, v_store: SparseStore,
                      k_window: torch.Tensor | None, v_window: torch.Tensor | None,
                      group: int, softmax_scale: float | None = None, out: torch.Tensor | None = None,
-                     nsplit: int = 0, stage_halves: int | None = None, variant: str = "auto",
-                     window_len: torch.Tensor | None = None, n_tokens: torch.Tensor | None = None) -> torch.Tensor:
+                     nsplit: int = 0, stage_halves: int | None = None,
+                     window_len: torch.Tensor | None = None, n_tokens: torch.Tensor | None = None,
+                     workspace: torch.Tensor | None = None) -> torch.Tensor:
     """Fused decode attention of one query token per q-head.
 
     q [n_kv_heads*group, 128] fp16; k_store / v_store hold the compressed tokens;
     k_window / v_window [n_kv_heads, W, 128] fp16 are the dense recent tokens (or None).
-    ``variant``: "auto" (size heuristic); "block" (fp16 coefficients), "block32" (fp32 coefficients),
-    "superblock", "stream" or "stream16" (stream kernel with fp16 coefficients) pins the kernel.
     ``window_len``: optional CUDA int32 tensor [1] with the number of valid window tokens (the window
     tensors then give the capacity); a captured launch can so be replayed while the window grows.
     ``n_tokens``: optional CUDA int32 tensor [1] with the number of compressed tokens to attend to (a multiple
     of 64, at most ``k_store.max_tokens``): the launch is then sized for the stores' capacity and keeps working
     while blocks are appended.  ``stage_halves`` must then cover every block still to come
-    (``64 * kept + 896`` always does).  Block kernel only.
-    Returns fp16 [n_kv_heads*group, 128].
+    (``64 * kept + 896`` does unless tokens have more than three ties at the pruning threshold).
+    ``workspace``: optional uint8 CUDA tensor from ``new_workspace`` (at least ``plan(...)`` bytes) owned by the caller;
+    required for calls captured into a CUDA graph next to other decode users, or issued on several streams.
+    One kernel launch.  Returns fp16 [n_kv_heads*group, 128].
     """
     n_kv = k_store.n_heads
     if q.dim() != 2 or q.shape != (n_kv * group, D) or q.dtype != torch.float16 or not q.is_cuda:
         raise RuntimeError("q must be CUDA float16 [n_kv_heads*group, 128]")
-    if q.stride(1) != 1:
+    if q.stride(1) != 1 or q.stride(0) % 2 or q.data_ptr() % 4:
         q = q.contiguous()
     L = k_store.tokens
     if v_store.tokens != L or v_store.n_heads != n_kv:
@@ -178,7 +205,6 @@ def decode_attention(q: torch.Tensor, k_store: SparseStore, v_store: SparseStore
         out = torch.empty((n_kv * group, D), dtype=torch.float16, device=q.device)
     if stage_halves is None and n_tokens is None:
         stage_halves = max(k_store.stage_hint(), v_store.stage_hint()) if L else 8
-    flags = {"auto": 0, "block": 1, "block32": 17, "superblock": 2, "stream": 4, "stream16": 12}[variant]
     wl = None if window_len is None else window_len.data_ptr()
     st = _dev_status(q.device)
     if n_tokens is not None:
@@ -188,29 +214,29 @@ def decode_attention(q: torch.Tensor, k_store: SparseStore, v_store: SparseStore
             raise RuntimeError("n_tokens on the device needs an explicit stage_halves bound")
         Lmax = min(k_store.max_tokens, v_store.max_tokens)
         _, nbytes = plan(n_kv, Lmax, W, group, nsplit)
-        ws = _workspace(q.device, nbytes)
+        ws = _take_workspace(workspace, q.device, nbytes)
         r = _lib.lib().mfar_decode_attention_fp16_dyn(
             q.data_ptr(), q.stride(0), n_kv, group,
             k_store.bitmaps.data_ptr(), k_store.tiles_cap, k_store.accum.data_ptr(), k_store.tiles_cap + 1,
-            k_store.nz.data_ptr(), None, k_store.nz_capacity,
+            k_store.nz.data_ptr(), None, k_store.nz_capacity, k_store.nz.numel(),
             v_store.bitmaps.data_ptr(), v_store.tiles_cap, v_store.accum.data_ptr(), v_store.tiles_cap + 1,
-            v_store.nz.data_ptr(), None, v_store.nz_capacity,
+            v_store.nz.data_ptr(), None, v_store.nz_capacity, v_store.nz.numel(),
             Lmax, n_tokens.data_ptr(), kw, vw, wh, wt, W, wl, float(softmax_scale), out.data_ptr(), out.stride(0),
-            ws.data_ptr(), ws.numel(), nsplit, stage_halves, flags, st.data_ptr(), _stream())
+            ws.data_ptr(), ws.numel(), nsplit, stage_halves, st.data_ptr(), _stream())
         _lib.check(r, "mfar_decode_attention_fp16_dyn")
         if _debug_check():
             check_device_status(q.device)
         return out
     _, nbytes = plan(n_kv, L, W, group, nsplit)
-    ws = _workspace(q.device, nbytes)
+    ws = _take_workspace(workspace, q.device, nbytes)
     r = _lib.lib().mfar_decode_attention_fp16(
         q.data_ptr(), q.stride(0), n_kv, group,
         k_store.bitmaps.data_ptr(), k_store.tiles_cap, k_store.accum.data_ptr(), k_store.tiles_cap + 1,
-        k_store.nz.data_ptr(), None, k_store.nz_capacity,
+        k_store.nz.data_ptr(), None, k_store.nz_capacity, k_store.nz.numel(),
         v_store.bitmaps.data_ptr(), v_store.tiles_cap, v_store.accum.data_ptr(), v_store.tiles_cap + 1,
-        v_store.nz.data_ptr(), None, v_store.nz_capacity,
+        v_store.nz.data_ptr(), None, v_store.nz_capacity, v_store.nz.numel(),
         L, kw, vw, wh, wt, W, wl, float(softmax_scale), out.data_ptr(), out.stride(0), ws.data_ptr(), ws.numel(),
-        nsplit, stage_halves, flags, st.data_ptr(), _stream())
+        nsplit, stage_halves, st.data_ptr(), _stream())
     _lib.check(r, "mfar_decode_attention_fp16")
     if _debug_check():
         check_device_status(q.device)

@@ -85,7 +85,7 @@ def _value(bmp, NZ_quant, tile_offsets, scales, zeros, P, probs_stride, M_Global
     n_kv = Batch_Size // groups
     tiles = M_Global * K_Global // 64
     _, nbytes = plan(n_kv, K_Global, 0, groups)
-    ws = _workspace(P.device, max(nbytes, n_kv * max(1, K_Global // 64) * groups * 132 * 4))
+    ws = _workspace(P.device, max(nbytes, 65536 + n_kv * max(1, K_Global // 64) * groups * 132 * 4))
     st = _dev_status(P.device)
     r = _lib.lib().mfar_value_output_quant(
         P.data_ptr(), probs_stride, n_kv, groups, bmp.data_ptr(), tiles, tile_offsets.data_ptr(), scales.data_ptr(),
@@ -145,7 +145,7 @@ def decode_attention_quant(q, kq: dict, vq: dict, n_tokens: int, k_window, v_win
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(D)
     out = torch.empty((n_kv * group, D), dtype=torch.float16, device=q.device)
-    ws = _workspace(q.device, n_kv * (max(1, n_tokens // 64) + 1) * group * 132 * 4)
+    ws = _workspace(q.device, 65536 + n_kv * (max(1, n_tokens // 64) + 1) * group * 132 * 4)
     st = _dev_status(q.device)
     # compact tensors hold exactly `tiles` tiles per head; an arena (QuantStore.as_dict) says how far apart heads are
     hs = int(kq.get("head_stride", tiles))

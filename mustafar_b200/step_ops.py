@@ -50,7 +50,8 @@ def rope_append(qkv: torch.Tensor, inv_freq: torch.Tensor, pos, slot, n_q_heads:
                 q_out: torch.Tensor, k_window: torch.Tensor, v_window: torch.Tensor) -> torch.Tensor:
     """qkv [B, (hq + 2*hkv) * 128] of one new token per sequence: RoPE on q and k at position ``pos``; q ->
     q_out [B*hq, 128]; k, v -> k_window / v_window [B*hkv, cap, 128] at token slot ``slot``.  pos and slot are
-    Python ints or CUDA int32 tensors of one element (read on the device at run time)."""
+    Python ints or CUDA int32 tensors of one element (read on the device at run time).  A device-resident slot
+    outside the window writes nothing and is reported by ``ops.check_device_status``."""
     _need(qkv, "rope_append qkv")
     _need(q_out, "rope_append q_out")
     B = qkv.shape[0]
@@ -73,13 +74,15 @@ def rope_append(qkv: torch.Tensor, inv_freq: torch.Tensor, pos, slot, n_q_heads:
         if int(v) < 0:
             raise RuntimeError(f"rope_append: negative {name}")
         return None, int(v)
+    from .ops import _dev_status
     pd, ph = dev_or_host(pos, "pos")
     sd, sh = dev_or_host(slot, "slot")
     if sd is None and sh >= k_window.shape[1]:
         raise RuntimeError("rope_append: slot beyond the window capacity")
     _lib.check(_lib.lib().mfar_rope_append_f16(qkv.data_ptr(), inv_freq.data_ptr(), pd, ph, sd, sh, B, n_q_heads, n_kv_heads,
                                                q_out.data_ptr(), k_window.data_ptr(), v_window.data_ptr(),
-                                               k_window.stride(0), k_window.stride(1), _stream()),
+                                               k_window.stride(0), k_window.stride(1), k_window.shape[1],
+                                               _dev_status(qkv.device).data_ptr(), _stream()),
                "mfar_rope_append_f16")
     return q_out
 

@@ -123,7 +123,7 @@ def _torch_prune(x, sparsity):
 
 @pytest.mark.parametrize("sparsity", [0.5, 0.7])
 def test_full_size_properties(mod, sparsity):
-    """BASELINE config 2 shape [64 heads, 8192 tokens, 128]: size-independent checks."""
+    """Prefill shape [8 sequences x 8 kv heads, 8192 tokens, 128]: size-independent checks."""
     g = torch.Generator(device="cuda").manual_seed(1234)
     x = torch.randn(64, 8192, 128, generator=g, device="cuda", dtype=torch.float32)
     x[:, :, [3, 40, 77, 120]] *= 10

@@ -82,18 +82,17 @@ def test_value_formulation(m, G, Bh, L):
 
 
 @pytest.mark.parametrize("G,Bh,L,W,s", [
-    (1, 32, 4096, 0, 0.7),        # BASELINE config 1: MHA, whole cache compressed
-    (4, 8, 4096, 128, 0.7),       # config 3 shape, batch 1
+    (1, 32, 4096, 0, 0.7),        # MHA, whole cache compressed, no window
+    (4, 8, 4096, 128, 0.7),       # Llama-3-8B GQA shape, one sequence
     (4, 4, 1024, 129, 0.5),
     (4, 2, 256, 384, 0.7),        # window at its largest (residual + 256)
     (2, 3, 192, 77, 0.7),
     (8, 1, 512, 5, 0.7),
-    (8, 3, 1024, 130, 0.7),       # 8 query heads per kv head: the block kernel runs them as two groups of 4
+    (8, 3, 1024, 130, 0.7),       # 8 query heads per kv head: run as two groups of 4
     (4, 2, 0, 200, 0.7),          # nothing compressed yet
     (1, 2, 64, 0, 0.0),           # unpruned: every tile full, worst-case stage
 ])
-@pytest.mark.parametrize("variant", ["block", "block32", "superblock", "stream", "stream16"])
-def test_fused_decode_attention(m, G, Bh, L, W, s, variant):
+def test_fused_decode_attention(m, G, Bh, L, W, s):
     if s > 0:
         kp, vp, ks, vs = build_cache(m, Bh, L, s, 31 + L + W)
     else:
@@ -105,8 +104,7 @@ def test_fused_decode_attention(m, G, Bh, L, W, s, variant):
     kw, vw = kw[:, :W], vw[:, :W]
     q = oracle.make_query(Bh * G, seed=8 + L)
     want = oracle.decode_attention_ref(q, kp, vp, kw, vw, G)
-    out = m.o.decode_attention(q.cuda(), ks, vs, kw.cuda() if W else None, vw.cuda() if W else None, G,
-                               variant=variant)
+    out = m.o.decode_attention(q.cuda(), ks, vs, kw.cuda() if W else None, vw.cuda() if W else None, G)
     assert oracle.rel_l2(out.float().cpu(), want) < TOL
     if L and W:
         # the reference's own order of fp16 roundings agrees to the same tolerance
@@ -114,12 +112,11 @@ def test_fused_decode_attention(m, G, Bh, L, W, s, variant):
         assert oracle.rel_l2(out.float().cpu(), model.float()) < 2 * TOL
 
 
-@pytest.mark.parametrize("variant", ["block", "block32", "superblock", "stream", "stream16"])
-def test_decode_split_invariance(m, variant):
-    kp, vp, ks, vs = build_cache(m, 2, 2048 + 64, 0.7, 5)     # 33 blocks: ragged last superblock
+def test_decode_split_invariance(m):
+    kp, vp, ks, vs = build_cache(m, 2, 2048 + 64, 0.7, 5)     # 33 blocks: a ragged last split
     kw, vw = oracle.make_kv(2, 128, seed=6)
     q = oracle.make_query(8, seed=7).cuda()
-    outs = [m.o.decode_attention(q, ks, vs, kw.cuda(), vw.cuda(), 4, nsplit=n, variant=variant).float()
+    outs = [m.o.decode_attention(q, ks, vs, kw.cuda(), vw.cuda(), 4, nsplit=n).float()
             for n in (1, 3, 32)]
     want = oracle.decode_attention_ref(q.cpu(), kp, vp, kw, vw, 4)
     assert oracle.rel_l2(outs[0].cpu(), want) < TOL
@@ -133,6 +130,30 @@ def test_small_stage_is_reported_not_silent(m):
     q = oracle.make_query(1, seed=1).cuda()
     with pytest.raises(RuntimeError):
         m.o.decode_attention(q, ks, vs, None, None, 1, stage_halves=64)
+
+
+@pytest.mark.parametrize("kind", ["misaligned", "beyond_extent", "negative"])
+def test_corrupt_offsets_are_reported_not_followed(m, kind):
+    """Offsets that the caller spliced wrongly (the reference-shaped ops take ``idx`` / ``NZ_Offset`` from torch
+    code) must set the status bit; the kernels skip the copy instead of issuing a misaligned or out-of-range one."""
+    kp, vp, ks, vs = build_cache(m, 2, 256, 0.7, 3)
+    q = oracle.make_query(2, seed=1).cuda()
+    bmp, nz, idx, off = reference_layout(ks)
+    idx = idx.clone()
+    if kind == "misaligned":
+        idx[1, 128] += 1            # block start no longer a multiple of 16 bytes
+    elif kind == "beyond_extent":
+        idx[1, 128:] += 1 << 20     # (aligned) ranges far past the end of NZ
+    else:
+        idx[0, 256] = -8
+    padded = torch.nn.functional.pad(q.view(2, 1, 128), (0, 0, 0, 7))
+    m.o.check_device_status()
+    with pytest.raises(RuntimeError):
+        m.o.mustafar_key_formulation(bmp, nz, idx, off, padded, 256, 128, 2, 1)
+    # the arena path: the same corruption inside a store
+    ks.accum[1, 128] += 1 if kind == "misaligned" else (1 << 28 if kind == "beyond_extent" else -(1 << 20))
+    with pytest.raises(RuntimeError):
+        m.o.decode_attention(q, ks, vs, None, None, 1)
 
 
 def test_op_argument_errors(m):

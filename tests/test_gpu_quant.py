@@ -177,3 +177,54 @@ def test_quant_store_reports_a_full_code_arena(m):
     st.append(k.cuda(), 0)
     with pytest.raises(MustafarError):
         st.check()
+
+
+def test_dequant_rounding_difference_is_bounded(m):
+    """The reference's kernels round every dequantised value to fp16 before the dot product
+    (kernel_quant/csrc/SpMM_Kernel_Quant.cuh:235-240); this library keeps (code - zero) * scale in fp32.  The two
+    conventions must stay within a small fraction of the 2e-3 tolerance of each other: the kernel's output is
+    compared with dense attention on the fp16-rounded values (the oracle's mode 0) and on unrounded fp32 values."""
+    Bh, G, L, bits = 2, 4, 1024, 2
+    k, v = oracle.make_kv(Bh, L, seed=77)
+    kp, vp = oracle.prune_ref(k, 0.7), oracle.prune_ref(v, 0.7)
+    kq = m.cq.compress_quant(k.cuda(), m.c.KEY, m.c.keep_rank(0.7), bits, 64)
+    vq = m.cq.compress_quant(v.cuda(), m.c.VALUE, m.c.keep_rank(0.7), bits, 64)
+    fk, fv = oracle.quant_compress_key_ref(kp, bits, 64), oracle.quant_compress_value_ref(vp, bits, 64)
+    kd16 = torch.from_numpy(oracle.dequant_key_ref(fk, L, bits=bits))
+    vd16 = torch.from_numpy(oracle.dequant_value_ref(fv, L, bits=bits))
+
+    def exact(fmt, to_dense):
+        """(code - zero) * scale without the fp16 rounding, through the oracle's own unpacking"""
+        import numpy as np
+        from oracle import quant_format as qf
+        tiles16 = qf._dequant_tiles(fmt, bits, 64, 0)
+        bitmaps = fmt["bitmaps"].view(np.uint64)
+        bit = ((bitmaps[..., None] >> np.arange(63, -1, -1, dtype=np.uint64)) & np.uint64(1)).astype(bool)
+        rank = np.cumsum(bit, axis=-1) - 1
+        cap = 32 // bits
+        word = fmt["tile_offsets"][..., None].astype(np.int64) + np.where(bit, rank // cap, 0)
+        packed = fmt["packed"].view(np.uint32)
+        q = (packed[np.minimum(word, packed.size - 1)] >> ((np.where(bit, rank, 0) % cap) * bits).astype(np.uint32)) & np.uint32(3)
+        s = fmt["scales"].astype(np.float32)[..., None]
+        z = fmt["zeros"].astype(np.float32)[..., None]
+        t = np.where(bit, (q.astype(np.float32) - z) * s, 0.0).astype(np.float32)
+        assert np.array_equal(t.astype(np.float16), tiles16)
+        return to_dense(t)
+
+    Bh_, T = fk["bitmaps"].shape
+    kd32 = torch.from_numpy(np.ascontiguousarray(exact(fk, lambda t: t.reshape(Bh, L // 64, 128, 64).transpose(0, 1, 3, 2))).reshape(Bh, L, 128))
+    vd32 = torch.from_numpy(np.ascontiguousarray(exact(fv, lambda t: t.reshape(Bh, L // 64, 2, 64, 64).transpose(0, 1, 3, 2, 4))).reshape(Bh, L, 128))
+    q = oracle.make_query(Bh * G, seed=3)
+    empty = torch.zeros(Bh, 0, 128, dtype=torch.float16)
+
+    def dense_attention(kd, vd):
+        kk, vv = kd.float().repeat_interleave(G, 0), vd.float().repeat_interleave(G, 0)
+        s = torch.bmm(kk, q.float().unsqueeze(-1)).squeeze(-1) / 128 ** 0.5
+        return torch.bmm(torch.softmax(s, -1).unsqueeze(1), vv).squeeze(1)
+
+    want16, want32 = dense_attention(kd16, vd16), dense_attention(kd32, vd32)
+    out = m.oq.decode_attention_quant(q.cuda(), kq, vq, L, None, None, G, bits).float().cpu()
+    between = oracle.rel_l2(want32, want16)
+    assert between < 5e-4, between                       # the two conventions themselves
+    assert oracle.rel_l2(out, want32) < 1e-3             # what the kernel computes
+    assert oracle.rel_l2(out, want16) < TOL              # what the reference's convention gives

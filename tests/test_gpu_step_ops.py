@@ -69,6 +69,27 @@ def test_rope_append(dev_state):
     assert kwin[:, mask].abs().sum() == 0 and vwin[:, mask].abs().sum() == 0
 
 
+def test_rope_append_slot_outside_window_is_reported_not_written():
+    """A device-resident slot equal to the window capacity (host and device counters out of step) must leave the
+    windows untouched and set the status bit; the query is still produced."""
+    from mustafar_b200 import ops, step_ops
+    B, hq, hkv, cap = 2, 4, 2, 8
+    g = torch.Generator(device="cuda").manual_seed(4)
+    qkv = torch.randn(B, (hq + 2 * hkv) * 128, generator=g, device="cuda").half()
+    guard = torch.zeros(B * hkv + 1, cap, 128, dtype=torch.float16, device="cuda")   # one spare head behind the window
+    kwin, vwin = guard[:B * hkv], torch.zeros(B * hkv, cap, 128, dtype=torch.float16, device="cuda")
+    q_out = torch.zeros(B * hq, 128, dtype=torch.float16, device="cuda")
+    st = torch.tensor([5, cap], dtype=torch.int32, device="cuda")
+    ops.check_device_status()
+    step_ops.rope_append(qkv, step_ops.rope_inv_freq(500000.0, "cuda"), st[0:1], st[1:2], hq, hkv, q_out, kwin, vwin)
+    with pytest.raises(RuntimeError):
+        ops.check_device_status()
+    assert guard.abs().sum() == 0 and vwin.abs().sum() == 0
+    assert q_out.abs().sum() > 0
+    with pytest.raises(RuntimeError):      # a host-side slot is refused before the launch
+        step_ops.rope_append(qkv, step_ops.rope_inv_freq(500000.0, "cuda"), 5, cap, hq, hkv, q_out, kwin, vwin)
+
+
 def test_silu_mul():
     from mustafar_b200 import step_ops
     g = torch.Generator(device="cuda").manual_seed(3)
