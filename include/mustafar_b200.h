@@ -284,11 +284,16 @@ int mfar_add_rmsnorm_f16(void* x, const void* delta, const void* weight, void* o
  * windows [batch*n_kv_heads][slot] (the torch.cat of :391 and :430 without the copy).  Position and slot are read from
  * pos_dev / slot_dev (int32 on the device) when those are not NULL, so that a captured CUDA graph can be replayed
  * while they advance; else from pos / slot.  window_capacity = token slots per window head: a slot outside
- * [0, window_capacity) writes nothing to the windows and sets MFAR_DEV_BADMETA in *dev_status (device uint32 or NULL). */
+ * [0, window_capacity) writes nothing to the windows and sets MFAR_DEV_BADMETA in *dev_status (device uint32 or NULL).
+ * prune_rank > 0 selects per-step pruning: the same launch prunes in place (rule of mfar_prune_fp16) the window token
+ * at slot - prune_back - 1 of every K and V head, i.e. the token that has just left the prune_back most recent ones
+ * (what the reference's torch path does at the end of every decode step,
+ * models/llama_mustafar_Kt_Mag_Vt_Mag.py:917-926, :1015-1024); windows 16-byte aligned, strides multiples of 8. */
 int mfar_rope_append_f16(const void* qkv, const float* inv_freq, const int32_t* pos_dev, int pos,
                          const int32_t* slot_dev, int slot, int batch, int n_q_heads, int n_kv_heads,
                          void* q_out, void* k_window, void* v_window, int64_t win_head_stride,
-                         int64_t win_token_stride, int window_capacity, uint32_t* dev_status, void* stream);
+                         int64_t win_token_stride, int window_capacity, int prune_rank, int prune_back,
+                         uint32_t* dev_status, void* stream);
 
 /* out[r, j] = fp16(silu(gate_up[r, j])) * gate_up[r, width + j], gate_up [rows, 2*width] (HF LlamaMLP). */
 int mfar_silu_mul_f16(const void* gate_up, void* out, int64_t rows, int width, void* stream);

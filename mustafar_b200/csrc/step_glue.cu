@@ -6,7 +6,7 @@
 //
 // Rounding follows the torch ops they replace, step by step: fp16 tensors, every elementwise op
 // computed in fp32 and rounded to fp16 once, RMS statistics in fp32.
-#include "common.cuh"
+#include "compress_common.cuh"
 
 namespace mfar {
 
@@ -67,15 +67,33 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(__half* x, const __hal
 // q heads: rotate, write to q_out [B*hq, 128].  k heads: rotate, write into the key window at token
 // slot widx.  v heads: copy into the value window.  Rotate-half convention, cos/sin rounded to fp16
 // before use, products and sums rounded to fp16 one by one (what the torch expression does).
+//
+// Per-step pruning (prune_rank > 0): the CTAs behind the batch * heads append CTAs prune, in place, the window token
+// that has just left the group of `prune_back` most recent ones, slot widx - prune_back - 1, of every K and V window
+// head: one thread pair per row, 32 rows per CTA.  It is the token the reference's torch path prunes at the end of the
+// previous step (models/llama_mustafar_Kt_Mag_Vt_Mag.py:917-926, :1015-1024); this step's attention sees it pruned.
 __global__ void __launch_bounds__(64) rope_append_kernel(const __half* qkv, const float* inv_freq, const int* pos_dev,
-                                                         int pos_host, const int* widx_dev, int widx_host, int hq, int hkv,
-                                                         __half* q_out, __half* kwin, __half* vwin, int64_t win_hs,
-                                                         int64_t win_ts, int capacity, unsigned* dev_status) {
+                                                         int pos_host, const int* widx_dev, int widx_host, int batch, int hq,
+                                                         int hkv, __half* q_out, __half* kwin, __half* vwin, int64_t win_hs,
+                                                         int64_t win_ts, int capacity, unsigned* dev_status, int prune_rank,
+                                                         int prune_back) {
     const int heads = hq + 2 * hkv;
+    const int widx = widx_dev ? *widx_dev : widx_host;
+    if (blockIdx.x >= static_cast<unsigned>(batch) * heads) {
+        const int row = (blockIdx.x - batch * heads) * 32 + (threadIdx.x >> 1), hh = threadIdx.x & 1;
+        const int slot = widx - prune_back - 1;
+        if (row >= 2 * batch * hkv || slot < 0 || slot >= capacity) return;   // both members of a pair leave together
+        __half* win = row < batch * hkv ? kwin : vwin;
+        __half* dst = win + static_cast<int64_t>(row % (batch * hkv)) * win_hs + slot * win_ts;
+        uint4 v[8];
+        load_prune_row(dst, hh, prune_rank, true, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) reinterpret_cast<uint4*>(dst)[2 * j + hh] = v[j];
+        return;
+    }
     const int b = blockIdx.x / heads, hd = blockIdx.x % heads, i = threadIdx.x;
     const __half* src = qkv + (static_cast<int64_t>(b) * heads + hd) * kD;
     const __half x1 = src[i], x2 = src[i + 64];
-    const int widx = widx_dev ? *widx_dev : widx_host;
     // a slot outside the window (host and device counters out of step) is reported, never written
     if (hd >= hq && (widx < 0 || widx >= capacity)) {
         if (i == 0 && dev_status) atomicOr(dev_status, MFAR_DEV_BADMETA);
@@ -135,17 +153,23 @@ extern "C" int mfar_add_rmsnorm_f16(void* x, const void* delta, const void* weig
 extern "C" int mfar_rope_append_f16(const void* qkv, const float* inv_freq, const int32_t* pos_dev, int pos,
                                     const int32_t* slot_dev, int slot, int batch, int n_q_heads, int n_kv_heads,
                                     void* q_out, void* k_window, void* v_window, int64_t win_head_stride,
-                                    int64_t win_token_stride, int window_capacity, uint32_t* dev_status, void* stream) {
+                                    int64_t win_token_stride, int window_capacity, int prune_rank, int prune_back,
+                                    uint32_t* dev_status, void* stream) {
     if (batch < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || pos < 0 || slot < 0 || window_capacity <= 0) return MFAR_ERR_ARG;
     if (!slot_dev && slot >= window_capacity) return MFAR_ERR_ARG;
+    if (prune_rank < 0 || prune_rank > kD || prune_back < 0) return MFAR_ERR_ARG;
+    if (prune_rank > 0 && ((reinterpret_cast<uintptr_t>(k_window) & 15) || (reinterpret_cast<uintptr_t>(v_window) & 15) ||
+                           (win_head_stride & 7) || (win_token_stride & 7)))
+        return MFAR_ERR_ALIGN;
     if (batch == 0) return MFAR_OK;
     if (!qkv || !inv_freq || !q_out || !k_window || !v_window) return MFAR_ERR_ARG;
-    const int64_t ctas = static_cast<int64_t>(batch) * (n_q_heads + 2 * n_kv_heads);
+    int64_t ctas = static_cast<int64_t>(batch) * (n_q_heads + 2 * n_kv_heads);
+    if (prune_rank > 0) ctas += (2ll * batch * n_kv_heads + 31) / 32;
     if (ctas > 0x7fffffffll) return MFAR_ERR_LIMIT;
     rope_append_kernel<<<static_cast<unsigned>(ctas), 64, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half*>(qkv), inv_freq, pos_dev, pos, slot_dev, slot, n_q_heads, n_kv_heads,
+        static_cast<const __half*>(qkv), inv_freq, pos_dev, pos, slot_dev, slot, batch, n_q_heads, n_kv_heads,
         static_cast<__half*>(q_out), static_cast<__half*>(k_window), static_cast<__half*>(v_window), win_head_stride,
-        win_token_stride, window_capacity, dev_status);
+        win_token_stride, window_capacity, dev_status, prune_rank, prune_back);
     return launch_status();
 }
 

@@ -7,7 +7,11 @@ What differs from the reference layer:
     window; nothing is ``torch.cat``-ed, padded to 8 rows or copied per step;
   * prune and compression are one kernel (prefill: the first ``((T - residual) // 256) * 256``
     tokens, ``:540-557``; decode: the oldest 256 tokens whenever the window reaches
-    ``residual + 256``, ``:445-519``);
+    ``residual + 256``, ``:445-519``).  That is ``prune_mode="block"``, the reference's kernel model.
+    ``prune_mode="step"`` prunes like the reference's torch path instead
+    (``models/llama_mustafar_Kt_Mag_Vt_Mag.py:917-926,1015-1024``): every decode step the token that leaves the
+    ``residual`` most recent ones is pruned in place in the window (inside the RoPE / append launch), so only
+    ``residual`` tokens are ever dense; compression still happens 256 tokens at a time, on rows already pruned;
   * q.K^T over compressed + window, softmax and P.V are one call per layer per step.
 Linear layers, RMSNorm, RoPE and the dense causal prefill attention are plain torch (cuBLAS /
 SDPA); they are outside the hot path this package accelerates.
@@ -72,13 +76,14 @@ class SparseLlama:
 
     def __init__(self, shape: LlamaShape, batch: int, max_tokens: int, device, sparsity: float = 0.7,
                  residual: int = 128, seed: int = 0, tp_rank: int = 0, tp_world: int = 1, dist=None,
-                 sparse: bool = True, cache_bits: int = 16):
+                 sparse: bool = True, cache_bits: int = 16, prune_mode: str = "block"):
         assert shape.n_kv_heads % tp_world == 0 and shape.ffn % tp_world == 0
         self.s, self.B, self.dev = shape, batch, torch.device(device)
         self.sparsity, self.residual, self.sparse = sparsity, residual, sparse
         # 16: pruned values kept as fp16; 2 or 4: pruned values quantised per tile (the reference's quantised model,
         # models/llama_mustafar_quant_kernel.py); the quantised cache runs its decode steps eagerly
-        assert cache_bits in (16, 2, 4)
+        assert cache_bits in (16, 2, 4) and prune_mode in ("block", "step")
+        self.step_prune = prune_mode == "step"
         self.cache_bits, self.quant = cache_bits, sparse and cache_bits != 16
         self.tp_rank, self.tp_world, self.dist = tp_rank, tp_world, dist
         self.hq = shape.n_q_heads // tp_world
@@ -191,11 +196,16 @@ class SparseLlama:
                     L.vs.append(vf[:, :Lc], self.rank_keep)
                 L.kwin[:, :T - Lc] = kf[:, Lc:]
                 L.vwin[:, :T - Lc] = vf[:, Lc:]
+                if self.step_prune and T - Lc > self.residual:      # only the newest `residual` tokens stay dense
+                    n = T - Lc - self.residual
+                    L.kwin[:, :n] = comp.prune(L.kwin[:, :n].contiguous(), self.sparsity)
+                    L.vwin[:, :n] = comp.prune(L.vwin[:, :n].contiguous(), self.sparsity)
             else:
                 L.ks[:, :T], L.vs[:, :T] = kf, vf
-                if Lc:
-                    L.ks[:, :Lc] = comp.prune(kf[:, :Lc].contiguous(), self.sparsity)
-                    L.vs[:, :Lc] = comp.prune(vf[:, :Lc].contiguous(), self.sparsity)
+                Lp = max(Lc, T - self.residual) if self.step_prune else Lc
+                if Lp > 0:
+                    L.ks[:, :Lp] = comp.prune(kf[:, :Lp].contiguous(), self.sparsity)
+                    L.vs[:, :Lp] = comp.prune(vf[:, :Lp].contiguous(), self.sparsity)
             del q, k, v, att
         self.tokens, self.compressed, self.wlen = T, Lc, T - Lc
         self._stage_hint = None
@@ -222,6 +232,10 @@ class SparseLlama:
             h = _rms(x, L.n1, self.s.rms_eps)
             q, k, v = self._qkv(L, h, pos)
             L.ks[:, t], L.vs[:, t] = k.reshape(B * self.hkv, D), v.reshape(B * self.hkv, D)
+            if self.step_prune and t - self.residual - 1 >= 0:
+                o = t - self.residual - 1
+                L.ks[:, o] = comp.prune(L.ks[:, o].contiguous(), self.sparsity)
+                L.vs[:, o] = comp.prune(L.vs[:, o].contiguous(), self.sparsity)
             kk = L.ks[:, :t + 1].float().repeat_interleave(self.G, dim=0)
             vv = L.vs[:, :t + 1].float().repeat_interleave(self.G, dim=0)
             sc = torch.bmm(kk, q.reshape(B * self.hq, D, 1).float()).squeeze(-1) / math.sqrt(D)
@@ -244,6 +258,7 @@ class SparseLlama:
             self._qbuf = torch.empty(B * self.hq, D, dtype=torch.float16, device=self.dev)
         hint = 0 if (dev_state or self.quant) else self._hint()
         w = self.wlen
+        pr = dict(prune_rank=self.rank_keep, prune_back=self.residual) if self.step_prune else {}
         tp = self.tp_world > 1
         x = self.embed[token]                     # [B, hidden], updated in place from here on
         delta = None
@@ -252,16 +267,16 @@ class SparseLlama:
             qkv = F.linear(h, L.wqkv)
             if dev_state:
                 step_ops.rope_append(qkv, self._inv_freq, self._state[0:1], self._state[1:2], self.hq, self.hkv,
-                                     self._qbuf, L.kwin, L.vwin)
+                                     self._qbuf, L.kwin, L.vwin, **pr)
                 att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin, L.vwin, self.G, stage_halves=self._stage_bound,
                                            window_len=self._state[2:3], n_tokens=self._state[3:4],
                                            workspace=self._decode_ws)
             elif self.quant:
-                step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin)
+                step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin, **pr)
                 att = ops_quant.decode_attention_quant(self._qbuf, L.ks.as_dict(), L.vs.as_dict(), self.compressed,
                                                        L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G, self.cache_bits)
             else:
-                step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin)
+                step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin, **pr)
                 att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G,
                                            stage_halves=hint, workspace=self._decode_ws)
             o = F.linear(att.view(B, self.hq * D), L.wo)
@@ -362,11 +377,17 @@ class SparseLlama:
         c = self.compressed
         for L in self.layers:
             if self.sparse:
-                L.ks.append(L.kwin[:, :256], self.rank_keep)
-                L.vs.append(L.vwin[:, :256], self.rank_keep)
+                rank = self.rank_keep
+                if self.step_prune:
+                    # slots 0..254 were pruned step by step; the last one would have been pruned by the next step
+                    L.kwin[:, 255] = comp.prune(L.kwin[:, 255].contiguous(), self.sparsity)
+                    L.vwin[:, 255] = comp.prune(L.vwin[:, 255].contiguous(), self.sparsity)
+                    rank = 0
+                L.ks.append(L.kwin[:, :256], rank)
+                L.vs.append(L.vwin[:, :256], rank)
                 L.kwin[:, :self.residual] = L.kwin[:, 256:].clone()
                 L.vwin[:, :self.residual] = L.vwin[:, 256:].clone()
-            else:
+            elif not self.step_prune:
                 L.ks[:, c:c + 256] = comp.prune(L.ks[:, c:c + 256].contiguous(), self.sparsity)
                 L.vs[:, c:c + 256] = comp.prune(L.vs[:, c:c + 256].contiguous(), self.sparsity)
         self.compressed += 256

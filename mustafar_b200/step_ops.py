@@ -47,11 +47,14 @@ def rope_inv_freq(theta: float, device) -> torch.Tensor:
 
 
 def rope_append(qkv: torch.Tensor, inv_freq: torch.Tensor, pos, slot, n_q_heads: int, n_kv_heads: int,
-                q_out: torch.Tensor, k_window: torch.Tensor, v_window: torch.Tensor) -> torch.Tensor:
+                q_out: torch.Tensor, k_window: torch.Tensor, v_window: torch.Tensor,
+                prune_rank: int = 0, prune_back: int = 0) -> torch.Tensor:
     """qkv [B, (hq + 2*hkv) * 128] of one new token per sequence: RoPE on q and k at position ``pos``; q ->
     q_out [B*hq, 128]; k, v -> k_window / v_window [B*hkv, cap, 128] at token slot ``slot``.  pos and slot are
     Python ints or CUDA int32 tensors of one element (read on the device at run time).  A device-resident slot
-    outside the window writes nothing and is reported by ``ops.check_device_status``."""
+    outside the window writes nothing and is reported by ``ops.check_device_status``.
+    ``prune_rank`` > 0 (see ``compression.keep_rank``): per-step pruning, the window token at ``slot - prune_back - 1``
+    of every K and V head is magnitude-pruned in place by the same launch."""
     _need(qkv, "rope_append qkv")
     _need(q_out, "rope_append q_out")
     B = qkv.shape[0]
@@ -82,6 +85,7 @@ def rope_append(qkv: torch.Tensor, inv_freq: torch.Tensor, pos, slot, n_q_heads:
     _lib.check(_lib.lib().mfar_rope_append_f16(qkv.data_ptr(), inv_freq.data_ptr(), pd, ph, sd, sh, B, n_q_heads, n_kv_heads,
                                                q_out.data_ptr(), k_window.data_ptr(), v_window.data_ptr(),
                                                k_window.stride(0), k_window.stride(1), k_window.shape[1],
+                                               int(prune_rank), int(prune_back),
                                                _dev_status(qkv.device).data_ptr(), _stream()),
                "mfar_rope_append_f16")
     return q_out

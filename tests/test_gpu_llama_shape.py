@@ -32,6 +32,37 @@ def test_sparse_model_matches_dense_pruned_model():
         L.ks.check(); L.vs.check()
 
 
+@pytest.mark.parametrize("graph", [False, True])
+def test_per_step_pruning_matches_dense_model_pruned_per_step(graph):
+    """prune_mode="step": the token leaving the 128 most recent ones is pruned in the window at every step (what the
+    reference's torch path does, models/llama_mustafar_Kt_Mag_Vt_Mag.py:917-926); the dense comparison model prunes
+    the same token at the same step.  Crosses a 256-token append, eager and as a replayed CUDA graph."""
+    from mustafar_b200.llama_shape import SparseLlama, tiny_shape
+    shape, B, prompt, steps = tiny_shape(), 2, 256 + 128 + 220, 50
+    kw = dict(batch=B, max_tokens=1024, device="cuda", sparsity=0.7, residual=128, seed=3, prune_mode="step")
+    sparse = SparseLlama(shape, sparse=True, **kw)
+    dense = SparseLlama(shape, sparse=False, **kw)
+    block = SparseLlama(shape, sparse=True, **{**kw, "prune_mode": "block"})
+    toks = torch.randint(0, shape.vocab, (B, prompt), generator=torch.Generator(device="cuda").manual_seed(1), device="cuda")
+    ls, ld, lb = sparse.prefill(toks), dense.prefill(toks), block.prefill(toks)
+    assert oracle.rel_l2(ls.float().cpu(), ld.float().cpu()) < 5e-3
+    differs = 0.0
+    for i in range(steps):
+        nxt = ld.argmax(-1)
+        ls, ld, lb = sparse.decode_step(nxt, graph=graph).clone(), dense.decode_step(nxt), block.decode_step(nxt)
+        assert oracle.rel_l2(ls.float().cpu(), ld.float().cpu()) < 5e-3, i
+        differs = max(differs, oracle.rel_l2(ls.float().cpu(), lb.float().cpu()))
+    assert sparse.compressed == 512 and sparse.wlen == dense.wlen
+    assert differs > 1e-3          # pruning the window tokens early is a different computation from block mode
+    from mustafar_b200 import ops
+    ops.check_device_status()
+    # behind the 128 most recent tokens (and the one the next step will prune first) every window row is pruned:
+    # at most 40 + ties nonzeros of 128
+    w = sparse.wlen
+    nnz = (sparse.layers[0].kwin[:, :w - 129] != 0).sum(-1)
+    assert int(nnz.max()) <= 44 and int((sparse.layers[0].kwin[:, w - 129:w] != 0).sum(-1).min()) > 100
+
+
 def test_graph_replay_matches_eager_steps():
     """Replaying the captured step (device-resident position / window length) gives the eager logits,
     across a block append that forces a re-capture."""

@@ -90,6 +90,50 @@ def test_rope_append_slot_outside_window_is_reported_not_written():
         step_ops.rope_append(qkv, step_ops.rope_inv_freq(500000.0, "cuda"), 5, cap, hq, hkv, q_out, kwin, vwin)
 
 
+def test_per_step_prune_builds_the_same_cache_as_block_mode():
+    """Feeding the same K / V stream token by token with per-step pruning (prune inside the append launch, then
+    compression of already pruned rows with prune_rank = 0) gives bit for bit the cache of block mode (dense window,
+    prune fused into the compression of the oldest 256 tokens)."""
+    from mustafar_b200 import compression as comp, ops, step_ops
+    B, hq, hkv, residual, rank = 2, 4, 2, 128, comp.keep_rank(0.7)
+    cap = residual + 256
+    Bh = B * hkv
+    g = torch.Generator(device="cuda").manual_seed(8)
+    inv = step_ops.rope_inv_freq(500000.0, "cuda")
+    stores = {}
+    for mode in ("block", "step"):
+        ks, vs = comp.SparseStore(Bh, 512, comp.KEY, "cuda"), comp.SparseStore(Bh, 512, comp.VALUE, "cuda")
+        kwin = torch.zeros(Bh, cap, 128, dtype=torch.float16, device="cuda")
+        vwin = torch.zeros_like(kwin)
+        q_out = torch.empty(B * hq, 128, dtype=torch.float16, device="cuda")
+        g.manual_seed(8)
+        w = 0
+        for t in range(2 * cap - residual):
+            qkv = torch.randn(B, (hq + 2 * hkv) * 128, generator=g, device="cuda").half()
+            extra = dict(prune_rank=rank, prune_back=residual) if mode == "step" else {}
+            step_ops.rope_append(qkv, inv, 0, w, hq, hkv, q_out, kwin, vwin, **extra)   # position 0: K is not rotated
+            w += 1
+            if w == cap:
+                r = rank
+                if mode == "step":
+                    kwin[:, 255] = comp.prune(kwin[:, 255].contiguous(), 0.7)
+                    vwin[:, 255] = comp.prune(vwin[:, 255].contiguous(), 0.7)
+                    r = 0
+                ks.append(kwin[:, :256], r)
+                vs.append(vwin[:, :256], r)
+                kwin[:, :residual] = kwin[:, 256:].clone()
+                vwin[:, :residual] = vwin[:, 256:].clone()
+                w = residual
+        ks.check(); vs.check()
+        stores[mode] = (ks, vs)
+    ops.check_device_status()
+    for a, b in zip(stores["block"], stores["step"]):
+        assert a.tokens == b.tokens == 512
+        assert torch.equal(a.bitmaps, b.bitmaps) and torch.equal(a.accum, b.accum)
+        for h, n in enumerate(a.packed_lengths().tolist()):
+            assert torch.equal(a.nz[h, :n].view(torch.int16), b.nz[h, :n].view(torch.int16)), h
+
+
 def test_silu_mul():
     from mustafar_b200 import step_ops
     g = torch.Generator(device="cuda").manual_seed(3)
