@@ -92,6 +92,11 @@ __device__ __forceinline__ unsigned ldg_nc_u16(const void* p) {
     asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
     return v;
 }
+__device__ __forceinline__ float4 ldcg_f32x4(const float* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
 __device__ __forceinline__ float ldcg_f32(const float* p) {
     float v;
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));
@@ -452,36 +457,49 @@ __global__ void __launch_bounds__(kAThreads, 4) decode_attn_kernel(DecodeParams 
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    // warp w merges heads w, w + 4: its lanes fetch the records' (m, l) in parallel, the weights go through shared
+    // memory (the reduction buffer is free again), then every lane sums four channels over the records
     const int nrec = p.nrec;
-    for (int g = 0; g < G; ++g) {
+    float* wgt = red;   // [G][nrec], nrec <= 129
+    for (int g = warp; g < G; g += kAWarps) {
         const float* base = record_ptr(p, G, h, 0, g);
         const int64_t step = static_cast<int64_t>(p.rec_group) * kPartialStride;
         float M = -INFINITY;
-        for (int s = 0; s < nrec; ++s) M = fmaxf(M, ldcg_f32(base + s * step + kPartM));
-        float o = 0.f, l = 0.f;
+        for (int s = lane; s < nrec; s += 32) M = fmaxf(M, ldcg_f32(base + s * step + kPartM));
+        M = warp_max_f32(M);
+        float l = 0.f;
+        for (int s = lane; s < nrec; s += 32) {
+            const float ms = ldcg_f32(base + s * step + kPartM);
+            const float w = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
+            l += w * ldcg_f32(base + s * step + kPartL);
+            wgt[g * nrec + s] = w;
+        }
+        l = warp_sum_f32(l);
+        __syncwarp();
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        const float* col = base + 4 * lane;
         int s = 0;
         for (; s + 4 <= nrec; s += 4) {
-            float ms[4], ls[4], vs[4];
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) v[u] = ldcg_f32x4(col + (s + u) * step);
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                ms[u] = ldcg_f32(base + (s + u) * step + kPartM);
-                ls[u] = ldcg_f32(base + (s + u) * step + kPartL);
-                vs[u] = ldcg_f32(base + (s + u) * step + tid);
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const float w = (ms[u] == -INFINITY) ? 0.f : fast_exp2(ms[u] - M);
-                l += w * ls[u];
-                o += w * vs[u];
+                const float w = wgt[g * nrec + s + u];
+                o.x += w * v[u].x; o.y += w * v[u].y; o.z += w * v[u].z; o.w += w * v[u].w;
             }
         }
         for (; s < nrec; ++s) {
-            const float m1 = ldcg_f32(base + s * step + kPartM);
-            const float w = (m1 == -INFINITY) ? 0.f : fast_exp2(m1 - M);
-            l += w * ldcg_f32(base + s * step + kPartL);
-            o += w * ldcg_f32(base + s * step + tid);
+            const float4 v = ldcg_f32x4(col + s * step);
+            const float w = wgt[g * nrec + s];
+            o.x += w * v.x; o.y += w * v.y; o.z += w * v.z; o.w += w * v.w;
         }
-        p.out[(static_cast<int64_t>(h) * G + g) * p.out_stride + tid] = __float2half_rn(l > 0.f ? o / l : 0.f);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __half* dst = p.out + (static_cast<int64_t>(h) * G + g) * p.out_stride + 4 * lane;
+        dst[0] = __float2half_rn(o.x * inv);
+        dst[1] = __float2half_rn(o.y * inv);
+        dst[2] = __float2half_rn(o.z * inv);
+        dst[3] = __float2half_rn(o.w * inv);
     }
 }
 
