@@ -211,7 +211,9 @@ int mfar_value_output_fp16(const void* probs, int64_t probs_stride, int n_kv_hea
 
 /* ------------------------------------------------------------------------- *
  * Decode over the quantised cache written by mfar_compress_quant (bits in {2,4},
- * qgroup in {64, 32}); dequantisation fp16((code - zero) * scale) is fused into the SpMV.
+ * qgroup in {64, 32}); dequantisation is fused into the SpMV.  The two single-product entries keep
+ * (code - zero) * scale in fp32 (no fp16 rounding of the dequantised value, which the reference applies: the
+ * outputs differ by less than 5e-4 relative L2, a test bounds it); the fused attention entry rounds like the reference.
  * Arguments as their fp16 counterparts; tile_offsets / scales / zeros share
  * meta_head_stride (tiles per head), packed_words bounds every access to `packed`.
  * ------------------------------------------------------------------------- */
@@ -237,17 +239,22 @@ int mfar_value_output_quant(const void* probs, int64_t probs_stride, int n_kv_he
                             int nsplit, uint32_t* dev_status, void* stream);
 
 /* Fused decode attention over the quantised cache + dense fp16 window (the quantised model's decode step,
- * models/llama_mustafar_quant_kernel.py:426-662, in one call).  workspace as mfar_decode_plan. */
+ * models/llama_mustafar_quant_kernel.py:426-662, in one call and one launch).  Every dequantised value is
+ * fp16((code - zero) * scale) with the subtraction and the product in fp32, the reference's default arithmetic
+ * (kernel_quant/csrc/SpMM_Kernel_Quant.cuh:235-240); the products with q / p accumulate in fp32.
+ * n_tokens_dev / window_len_dev: NULL, or device int32 holding the current compressed length (a multiple of 64,
+ * at most n_tokens, which then sizes the grid) / window length (at most window), read when the kernel runs, so that a
+ * captured launch can be replayed while the cache grows.  workspace as mfar_decode_plan. */
 int mfar_decode_attention_quant(
     const void* q, int64_t q_stride, int n_kv_heads, int group,
     const int64_t* k_bitmaps, const int32_t* k_tile_offsets, const void* k_scales, const void* k_zeros,
     const int32_t* k_packed, int64_t k_packed_words,
     const int64_t* v_bitmaps, const int32_t* v_tile_offsets, const void* v_scales, const void* v_zeros,
     const int32_t* v_packed, int64_t v_packed_words,
-    int64_t bmp_head_stride, int64_t meta_head_stride, int n_tokens, int bits, int qgroup,
+    int64_t bmp_head_stride, int64_t meta_head_stride, int n_tokens, const int32_t* n_tokens_dev, int bits, int qgroup,
     const void* k_window, const void* v_window, int64_t win_head_stride, int64_t win_token_stride, int window,
-    float softmax_scale, void* out, int64_t out_stride, void* workspace, size_t workspace_bytes, int nsplit,
-    uint32_t* dev_status, void* stream);
+    const int32_t* window_len_dev, float softmax_scale, void* out, int64_t out_stride, void* workspace,
+    size_t workspace_bytes, int nsplit, uint32_t* dev_status, void* stream);
 
 /* mfar_decode_attention_fp16 for callers that replay a captured launch while the cache grows: the number of
  * compressed tokens is read from n_tokens_dev (int32 on the device, a multiple of 64) when the kernel runs;

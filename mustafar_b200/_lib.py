@@ -50,8 +50,8 @@ SIGNATURES = {
     "mfar_decode_attention_quant": (_i32, [_vp, _i64, _i32, _i32,
                                            _vp, _vp, _vp, _vp, _vp, _i64,
                                            _vp, _vp, _vp, _vp, _vp, _i64,
-                                           _i64, _i64, _i32, _i32, _i32,
-                                           _vp, _vp, _i64, _i64, _i32,
+                                           _i64, _i64, _i32, _vp, _i32, _i32,
+                                           _vp, _vp, _i64, _i64, _i32, _vp,
                                            _f32, _vp, _i64, _vp, _sz, _i32, _vp, _vp]),
     "mfar_add_rmsnorm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp]),
     "mfar_rope_append_f16": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i32,

@@ -19,6 +19,13 @@
 // query heads (up to 8) are the n dimension.  The multiply-accumulate of a 64-token block is 64 tensor-core
 // instructions per CTA; what remains, and what bounds the kernel, is the shared-memory traffic of the
 // predicated loads.
+//
+// The same kernel serves the quantised cache (QBITS = 2 or 4): there a tile's code words, bitmap, scale and zero-point
+// are staged by the threads themselves (4-byte cp.async, one tile of each tensor per thread, one block ahead); a lane
+// takes the codes of its byte out of a 32-bit window that starts at its rank, turns every code into
+// fp16((code - zero) * scale) with the subtraction and the product in fp32 - the reference's arithmetic
+// (kernel_quant/csrc/SpMM_Kernel_Quant.cuh:235-240) - and packs the two tiles' values into the same fragments.
+// No per-position shared-memory load is left, so that variant is bound by instruction issue.
 #include "decode_common.cuh"
 
 namespace mfar {
@@ -36,13 +43,14 @@ __host__ __device__ inline size_t attn_stage_bytes(int cap) {
 struct AttnLayout {
     size_t stages, bars, ps, red, alpha, koff, voff, kblk, vblk, total;
     size_t s_kbm, s_vbm, s_kval, s_vval;
-    __host__ __device__ AttnLayout(int cap, int G) {
+    // qbuf_bytes > 0: quantised cache, a stage is two QBuf (K then V) instead of bitmaps + packed halves
+    __host__ __device__ AttnLayout(int cap, int G, size_t qbuf_bytes = 0) {
         s_kbm = 0;
         s_vbm = 1024;
         s_kval = 2048;
         s_vval = 2048 + (static_cast<size_t>(cap) + kSlackHalves) * 2;
         size_t o = 0;
-        stages = o; o += kAStages * attn_stage_bytes(cap);
+        stages = o; o += kAStages * (qbuf_bytes ? 2 * qbuf_bytes : attn_stage_bytes(cap));
         bars = o;   o += 64;
         ps = o;     o += 8 * kPsStride * 2;
         red = o;    o += static_cast<size_t>(kAWarps) * G * kD * 4;   // score planes, later the output reduction
@@ -82,6 +90,54 @@ __device__ __forceinline__ void expand_pair(uint4 bm, const unsigned short* va, 
     }
 }
 
+
+__device__ __forceinline__ void cp_async4(void* dst_smem, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst_smem)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// Quantised counterpart of expand_pair: byte `sel` of tiles c and c + 1 of a staged block.  A lane's codes are
+// consecutive in the tile's code words from bit rank * BITS on; every set bit takes the next code.
+template <int BITS, bool GROUP32>
+__device__ __forceinline__ void expand_pair_q(const QBuf<BITS>& b, int c, unsigned sel, unsigned mh, unsigned ml,
+                                              unsigned (&r)[8]) {
+    constexpr unsigned MASK = (1u << BITS) - 1u;
+    constexpr int WPT = QBuf<BITS>::WPT;
+    const uint4 bm = *reinterpret_cast<const uint4*>(&b.bm[c]);
+    const uint4 sz = *reinterpret_cast<const uint4*>(&b.sz[2 * c]);   // (scale | zero << 16): A group 0, 1; B group 0, 1
+    const unsigned ba = __byte_perm(bm.x, bm.y, sel), bb = __byte_perm(bm.z, bm.w, sel);
+    int ra = __popc(bm.y & mh) + __popc(bm.x & ml), rb = __popc(bm.w & mh) + __popc(bm.z & ml);
+    const unsigned oa = static_cast<unsigned>(ra) * BITS, ob = static_cast<unsigned>(rb) * BITS;
+    const unsigned* wa = b.words + c * WPT + (oa >> 5);
+    const unsigned* wb = b.words + (c + 1) * WPT + (ob >> 5);
+    unsigned wina = __funnelshift_r(wa[0], wa[1], oa & 31u), winb = __funnelshift_r(wb[0], wb[1], ob & 31u);
+    auto scale_of = [](unsigned x) { return __half2float(__ushort_as_half(static_cast<unsigned short>(x & 0xffffu))); };
+    // code - zero exactly: the code is or-ed into the mantissa of 2^23, the zero-point is offset by 2^23 as well
+    auto zero_of = [](unsigned x) { return 8388608.f + __half2float(__ushort_as_half(static_cast<unsigned short>(x >> 16))); };
+    const float sa0 = scale_of(sz.x), za0 = zero_of(sz.x), sb0 = scale_of(sz.z), zb0 = zero_of(sz.z);
+    float sa1 = sa0, za1 = za0, sb1 = sb0, zb1 = zb0;
+    if (GROUP32) { sa1 = scale_of(sz.y); za1 = zero_of(sz.y); sb1 = scale_of(sz.w); zb1 = zero_of(sz.w); }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float va = 0.f, vb = 0.f;
+        if (ba & (0x80u >> i)) {
+            const bool second = GROUP32 && ra >= 32;   // nonzeros 32.. of a tile use the second scale / zero-point
+            va = (__uint_as_float(0x4b000000u | (wina & MASK)) - (second ? za1 : za0)) * (second ? sa1 : sa0);
+            wina >>= BITS;
+            if (GROUP32) ++ra;
+        }
+        if (bb & (0x80u >> i)) {
+            const bool second = GROUP32 && rb >= 32;
+            vb = (__uint_as_float(0x4b000000u | (winb & MASK)) - (second ? zb1 : zb0)) * (second ? sb1 : sb0);
+            winb >>= BITS;
+            if (GROUP32) ++rb;
+        }
+        const __half2 h2 = __floats2half2_rn(va, vb);
+        r[i] = *reinterpret_cast<const unsigned*>(&h2);
+    }
+}
+
 __device__ __forceinline__ unsigned ldg_nc_u32(const void* p) {
     unsigned v;
     asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
@@ -110,10 +166,12 @@ __device__ __forceinline__ float* record_ptr(const DecodeParams& p, int G, int h
     return p.ws + ((static_cast<int64_t>(h * sets + g / rg) * p.nrec + split) * rg + (g % rg)) * kPartialStride;
 }
 
-template <int G>
+template <int G, int QBITS, bool GROUP32>
 __global__ void __launch_bounds__(kAThreads, 4) decode_attn_kernel(DecodeParams p) {
+    constexpr bool QUANT = QBITS != 0;
+    using QB = QBuf<QUANT ? QBITS : 2>;
     extern __shared__ __align__(128) unsigned char smem[];
-    const AttnLayout lay(p.cap, G);
+    const AttnLayout lay(p.cap, G, QUANT ? sizeof(QB) : 0);
     unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + lay.bars);
     unsigned short* ps = reinterpret_cast<unsigned short*>(smem + lay.ps);    // [8][kPsStride] probabilities, fp16
     float* red = reinterpret_cast<float*>(smem + lay.red);                     // [warp][G][kPlaneStride] scores
@@ -156,9 +214,9 @@ __global__ void __launch_bounds__(kAThreads, 4) decode_attn_kernel(DecodeParams 
             for (int j = 0; j < 2; ++j) qb[kg][j] = ldg_nc_u32(qrow + kg * 16 + j * 8);
     }
     for (int i = tid; i < 8 * kPsStride / 2; i += kAThreads) reinterpret_cast<unsigned*>(ps)[i] = 0u;
-    const int* kacc = p.k.acc + h * p.k.acc_hs;
-    const int* vacc = p.v.acc + h * p.v.acc_hs;
-    if (!is_window) {
+    const int* kacc = QUANT ? nullptr : p.k.acc + h * p.k.acc_hs;
+    const int* vacc = QUANT ? nullptr : p.v.acc + h * p.v.acc_hs;
+    if (!QUANT && !is_window) {
         for (int i = tid; i <= nb; i += kAThreads) {
             kblk[i] = kacc[static_cast<int64_t>(blk0 + i) * kTilesPerBlock];
             vblk[i] = vacc[static_cast<int64_t>(blk0 + i) * kTilesPerBlock];
@@ -170,8 +228,8 @@ __global__ void __launch_bounds__(kAThreads, 4) decode_attn_kernel(DecodeParams 
     }
     __syncthreads();
 
-    const int64_t k_head0 = p.k.nz_off ? 8ll * p.k.nz_off[h] : h * p.k.nz_hs;
-    const int64_t v_head0 = p.v.nz_off ? 8ll * p.v.nz_off[h] : h * p.v.nz_hs;
+    const int64_t k_head0 = QUANT ? 0 : (p.k.nz_off ? 8ll * p.k.nz_off[h] : h * p.k.nz_hs);
+    const int64_t v_head0 = QUANT ? 0 : (p.v.nz_off ? 8ll * p.v.nz_off[h] : h * p.v.nz_hs);
     const __half* knz = p.k.nz + k_head0;
     const __half* vnz = p.v.nz + v_head0;
     const size_t stg = attn_stage_bytes(p.cap);
@@ -210,11 +268,54 @@ __global__ void __launch_bounds__(kAThreads, 4) decode_attn_kernel(DecodeParams 
         voff[(i & 1) * 128 + tid] = min(static_cast<unsigned>(2 * (nxt_v - vblk[i])), lim);
     };
 
+    // quantised cache: thread t owns K tile t and V tile t of a block; their metadata travels through registers
+    // one block ahead, the code words go straight to the tile's slot of the stage
+    struct Meta { uint2 bm; int off; unsigned sz[2]; };
+    Meta mk{}, mv{};
+    auto q_load_meta = [&](const QSparse& sp, int i, Meta& m) {
+        const int64_t t = static_cast<int64_t>(blk0 + i) * kTilesPerBlock + tid;
+        const unsigned long long bmw = sp.bmp[h * sp.bmp_hs + t];
+        m.bm = make_uint2(static_cast<unsigned>(bmw), static_cast<unsigned>(bmw >> 32));
+        const int64_t mi = h * sp.meta_hs + t;
+        m.off = sp.tile_off[mi];
+        const int ngrp = GROUP32 ? 2 : 1;
+        m.sz[1] = 0u;
+        for (int g = 0; g < ngrp; ++g)
+            m.sz[g] = static_cast<unsigned>(__half_as_ushort(sp.scales[mi * ngrp + g])) |
+                      (static_cast<unsigned>(__half_as_ushort(sp.zeros[mi * ngrp + g])) << 16);
+    };
+    auto q_stage = [&](const QSparse& sp, const Meta& m, QB& b) {
+        constexpr int CAPW = 32 / (QUANT ? QBITS : 2);
+        b.bm[tid] = m.bm;
+        b.sz[2 * tid] = m.sz[0];
+        b.sz[2 * tid + 1] = m.sz[1];
+        const int n = (__popc(m.bm.x) + __popc(m.bm.y) + CAPW - 1) / CAPW;
+        if (m.off < 0 || static_cast<long long>(m.off) + n > sp.packed_words) {
+            if (n > 0 && p.dev_status) atomicOr(p.dev_status, MFAR_DEV_BADMETA);
+            b.bm[tid] = make_uint2(0u, 0u);     // the tile contributes nothing
+            return;
+        }
+        const unsigned* src = sp.packed + m.off;
+        for (int j = 0; j < n; ++j) cp_async4(&b.words[tid * QB::WPT + j], src + j);
+    };
+    auto qbuf = [&](int i, int which) -> QB& {
+        return *reinterpret_cast<QB*>(smem + lay.stages + (static_cast<size_t>(i % kAStages) * 2 + which) * sizeof(QB));
+    };
+
     if (!is_window && nb > 0) {
-        if (tid == 0)
-            for (int i = 0; i < min(nb, kAStages - 1); ++i) issue(i);
-        fetch_offsets(0);
-        store_offsets(0);
+        if (QUANT) {
+            q_load_meta(p.kq, 0, mk);
+            q_load_meta(p.vq, 0, mv);
+            q_stage(p.kq, mk, qbuf(0, 0));
+            q_stage(p.vq, mv, qbuf(0, 1));
+            cp_async_commit();
+            if (nb > 1) { q_load_meta(p.kq, 1, mk); q_load_meta(p.vq, 1, mv); }
+        } else {
+            if (tid == 0)
+                for (int i = 0; i < min(nb, kAStages - 1); ++i) issue(i);
+            fetch_offsets(0);
+            store_offsets(0);
+        }
     }
     __syncthreads();
 
@@ -243,12 +344,27 @@ __global__ void __launch_bounds__(kAThreads, 4) decode_attn_kernel(DecodeParams 
         const unsigned* vo = voff + (i & 1) * 128;
 
         if (!is_window) {
-            if (i + 1 < nb) fetch_offsets(i + 1);
-            if (!mbar_wait(&bars[i % kAStages], (i / kAStages) & 1)) timed_out = true;
+            if (QUANT) {
+                cp_async_wait_all();
+            } else {
+                if (i + 1 < nb) fetch_offsets(i + 1);
+                if (!mbar_wait(&bars[i % kAStages], (i / kAStages) & 1)) timed_out = true;
+            }
         }
         if (__syncthreads_or(timed_out)) { timed_out = true; break; }   // also publishes the stage hand-off below
         // every warp is done with block i-1, so its stage can take block i + kAStages - 1
-        if (!is_window && tid == 0 && i + kAStages - 1 < nb) issue(i + kAStages - 1);
+        if (!is_window) {
+            if (QUANT) {
+                if (i + 1 < nb) {
+                    q_stage(p.kq, mk, qbuf(i + 1, 0));
+                    q_stage(p.vq, mv, qbuf(i + 1, 1));
+                    cp_async_commit();
+                    if (i + 2 < nb) { q_load_meta(p.kq, i + 2, mk); q_load_meta(p.vq, i + 2, mv); }
+                }
+            } else if (tid == 0 && i + kAStages - 1 < nb) {
+                issue(i + kAStages - 1);
+            }
+        }
 
         // ------------------------------------------------------------ K phase: this warp's 32 channels x 64 tokens
         // dk[j]: rows = tokens 8*tb + j (d0, d1) and 8*tb + j + 4 (d2, d3); columns = heads 2*cp, 2*cp+1
@@ -261,17 +377,23 @@ __global__ void __launch_bounds__(kAThreads, 4) decode_attn_kernel(DecodeParams 
 #pragma unroll
             for (int kg = 0; kg < 2; ++kg) {
                 unsigned r1[8], r2[8];
-                {
+                if (QUANT) {
                     const int c = warp * 32 + kg * 16 + 2 * cp;
-                    const uint4 bm = *reinterpret_cast<const uint4*>(kbm + c);
-                    const uint2 of = *reinterpret_cast<const uint2*>(ko + c);
-                    expand_pair(bm, kval + of.x, kval + of.y, sel, mh, ml, r1);
-                }
-                {
-                    const int c = warp * 32 + kg * 16 + 8 + 2 * cp;
-                    const uint4 bm = *reinterpret_cast<const uint4*>(kbm + c);
-                    const uint2 of = *reinterpret_cast<const uint2*>(ko + c);
-                    expand_pair(bm, kval + of.x, kval + of.y, sel, mh, ml, r2);
+                    expand_pair_q<QB::BITS, GROUP32>(qbuf(i, 0), c, sel, mh, ml, r1);
+                    expand_pair_q<QB::BITS, GROUP32>(qbuf(i, 0), c + 8, sel, mh, ml, r2);
+                } else {
+                    {
+                        const int c = warp * 32 + kg * 16 + 2 * cp;
+                        const uint4 bm = *reinterpret_cast<const uint4*>(kbm + c);
+                        const uint2 of = *reinterpret_cast<const uint2*>(ko + c);
+                        expand_pair(bm, kval + of.x, kval + of.y, sel, mh, ml, r1);
+                    }
+                    {
+                        const int c = warp * 32 + kg * 16 + 8 + 2 * cp;
+                        const uint4 bm = *reinterpret_cast<const uint4*>(kbm + c);
+                        const uint2 of = *reinterpret_cast<const uint2*>(ko + c);
+                        expand_pair(bm, kval + of.x, kval + of.y, sel, mh, ml, r2);
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) mma16816(dk[j], r1[j], r1[j + 4], r2[j], r2[j + 4], qb[kg][0], qb[kg][1]);
@@ -344,7 +466,7 @@ __global__ void __launch_bounds__(kAThreads, 4) decode_attn_kernel(DecodeParams 
                 if (lane == 0) alpha_s[g] = a;
             }
         }
-        if (!is_window && i + 1 < nb) store_offsets(i + 1);
+        if (!QUANT && !is_window && i + 1 < nb) store_offsets(i + 1);
         __syncthreads();
 
         // ------------------------------------------------------------ V phase: this warp's 16 tokens x 128 channels
@@ -369,17 +491,23 @@ __global__ void __launch_bounds__(kAThreads, 4) decode_attn_kernel(DecodeParams 
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
                 unsigned r1[8], r2[8];
-                {
+                if (QUANT) {
                     const int t = hf * 64 + warp * 16 + 2 * cp;
-                    const uint4 bm = *reinterpret_cast<const uint4*>(vbm + t);
-                    const uint2 of = *reinterpret_cast<const uint2*>(vo + t);
-                    expand_pair(bm, vval + of.x, vval + of.y, sel, mh, ml, r1);
-                }
-                {
-                    const int t = hf * 64 + warp * 16 + 8 + 2 * cp;
-                    const uint4 bm = *reinterpret_cast<const uint4*>(vbm + t);
-                    const uint2 of = *reinterpret_cast<const uint2*>(vo + t);
-                    expand_pair(bm, vval + of.x, vval + of.y, sel, mh, ml, r2);
+                    expand_pair_q<QB::BITS, GROUP32>(qbuf(i, 1), t, sel, mh, ml, r1);
+                    expand_pair_q<QB::BITS, GROUP32>(qbuf(i, 1), t + 8, sel, mh, ml, r2);
+                } else {
+                    {
+                        const int t = hf * 64 + warp * 16 + 2 * cp;
+                        const uint4 bm = *reinterpret_cast<const uint4*>(vbm + t);
+                        const uint2 of = *reinterpret_cast<const uint2*>(vo + t);
+                        expand_pair(bm, vval + of.x, vval + of.y, sel, mh, ml, r1);
+                    }
+                    {
+                        const int t = hf * 64 + warp * 16 + 8 + 2 * cp;
+                        const uint4 bm = *reinterpret_cast<const uint4*>(vbm + t);
+                        const uint2 of = *reinterpret_cast<const uint2*>(vo + t);
+                        expand_pair(bm, vval + of.x, vval + of.y, sel, mh, ml, r2);
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) mma16816(dv[hf][j], r1[j], r1[j + 4], r2[j], r2[j + 4], pb0, pb1);
@@ -503,30 +631,42 @@ __global__ void __launch_bounds__(kAThreads, 4) decode_attn_kernel(DecodeParams 
     }
 }
 
-template <int G>
+template <int G, int QBITS, bool GROUP32>
 static int launch_attn(const DecodeParams& p, int n_kv_heads, int grid_x, cudaStream_t s) {
-    const AttnLayout lay(p.cap, G);
+    const AttnLayout lay(p.cap, G, QBITS ? sizeof(QBuf<QBITS ? QBITS : 2>) : 0);
     static size_t configured[64] = {0};   // largest dynamic shared memory size opted into so far, per device
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MFAR_ERR_LAUNCH;
     if (lay.total > configured[dev]) {
-        if (cudaFuncSetAttribute(decode_attn_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(decode_attn_kernel<G, QBITS, GROUP32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(lay.total)) != cudaSuccess)
             return MFAR_ERR_LAUNCH;
         configured[dev] = lay.total;
     }
-    decode_attn_kernel<G><<<dim3(grid_x, n_kv_heads), kAThreads, lay.total, s>>>(p);
+    decode_attn_kernel<G, QBITS, GROUP32><<<dim3(grid_x, n_kv_heads), kAThreads, lay.total, s>>>(p);
     return launch_status();
 }
 
-int launch_decode_attn(const DecodeParams& p, int G, int n_kv_heads, int grid_x, cudaStream_t s) {
+template <int QBITS, bool GROUP32>
+static int dispatch_attn(const DecodeParams& p, int G, int n_kv_heads, int grid_x, cudaStream_t s) {
     switch (G) {
-        case 1: return launch_attn<1>(p, n_kv_heads, grid_x, s);
-        case 2: return launch_attn<2>(p, n_kv_heads, grid_x, s);
-        case 4: return launch_attn<4>(p, n_kv_heads, grid_x, s);
-        case 8: return launch_attn<8>(p, n_kv_heads, grid_x, s);
+        case 1: return launch_attn<1, QBITS, GROUP32>(p, n_kv_heads, grid_x, s);
+        case 2: return launch_attn<2, QBITS, GROUP32>(p, n_kv_heads, grid_x, s);
+        case 4: return launch_attn<4, QBITS, GROUP32>(p, n_kv_heads, grid_x, s);
+        case 8: return launch_attn<8, QBITS, GROUP32>(p, n_kv_heads, grid_x, s);
         default: return MFAR_ERR_ARG;
     }
+}
+
+int launch_decode_attn(const DecodeParams& p, int G, int n_kv_heads, int grid_x, cudaStream_t s) {
+    return dispatch_attn<0, false>(p, G, n_kv_heads, grid_x, s);
+}
+
+int launch_decode_attn_quant(const DecodeParams& p, int G, int bits, bool group32, int n_kv_heads, int grid_x,
+                             cudaStream_t s) {
+    if (bits == 2) return group32 ? dispatch_attn<2, true>(p, G, n_kv_heads, grid_x, s) : dispatch_attn<2, false>(p, G, n_kv_heads, grid_x, s);
+    if (bits == 4) return group32 ? dispatch_attn<4, true>(p, G, n_kv_heads, grid_x, s) : dispatch_attn<4, false>(p, G, n_kv_heads, grid_x, s);
+    return MFAR_ERR_ARG;
 }
 
 int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G, const void* kwin, const void* vwin,

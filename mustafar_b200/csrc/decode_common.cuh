@@ -166,8 +166,29 @@ struct Sparse {
     int64_t nz_extent;   // halves addressable from nz (0 = unknown: the extent check is skipped)
 };
 
+// one tensor of the quantised cache (mfar_compress_quant)
+struct QSparse {
+    const unsigned long long* bmp;
+    const int* tile_off;
+    const __half* scales;
+    const __half* zeros;
+    const unsigned* packed;
+    int64_t bmp_hs, meta_hs;
+    long long packed_words;
+};
+
+template <int BITS_>
+struct QBuf {   // one staged tensor of one 64-token block of the quantised cache
+    static constexpr int BITS = BITS_;
+    static constexpr int WPT = 64 * BITS_ / 32;  // words per tile slot
+    uint2 bm[128];
+    unsigned sz[128 * 2];                        // (scale | zero << 16) per group
+    unsigned words[128 * WPT + 4];
+};
+
 struct DecodeParams {
     Sparse k, v;
+    QSparse kq, vq;        // fused attention over the quantised cache (k, v unused then)
     const __half* q;       // [Bq][q_stride]
     int64_t q_stride;
     const __half* kwin;    // dense window [Bh][W][128]
@@ -215,6 +236,9 @@ __device__ __forceinline__ bool block_range_bad(int blk, int nxt, unsigned capb,
 
 // fused decode attention (decode_attn.cu): grid (grid_x, n_kv_heads); G in {1, 2, 4, 8}
 int launch_decode_attn(const DecodeParams& p, int G, int n_kv_heads, int grid_x, cudaStream_t s);
+// the same over the quantised cache p.kq / p.vq: bits in {2, 4}, group32 = a second scale / zero-point from nonzero 32 on
+int launch_decode_attn_quant(const DecodeParams& p, int G, int bits, bool group32, int n_kv_heads, int grid_x,
+                             cudaStream_t s);
 // merge of the split-KV records (normalise = 1) or plain sum (normalise = 0), one CTA per q head
 int launch_combine(const float* ws, int nrec, int G, int normalise, void* out, int64_t out_stride, int n_q_heads,
                    cudaStream_t s);

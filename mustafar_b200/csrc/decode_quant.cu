@@ -1,7 +1,8 @@
-// Decode over the quantised bitmap cache (2- or 4-bit codes, per-tile or per-32-nonzero
-// scale / zero-point), dequantisation fused into the SpMV.
+// Single-product kernels over the quantised bitmap cache (2- or 4-bit codes, per-tile or per-32-nonzero
+// scale / zero-point) behind the reference-shaped ops, and the entry points of the quantised cache.  The fused
+// attention over this cache is the QBITS instantiation of decode_attn.cu.
 //
-// Same work split as the fp16 block kernel (decode.cu): a CTA of 4 warps walks 64-token
+// Same work split as the fp16 single-product kernels (decode.cu): a CTA of 4 warps walks 64-token
 // blocks of one kv head for all G query heads; a lane owns one byte of a tile's bitmap.
 // Differences:
 //   * staging: every thread copies the metadata of "its" K tile and V tile (bitmap, offset,
@@ -28,16 +29,6 @@ constexpr int kQThreads = kQWarps * 32;
 constexpr int kQPlanes = kQWarps * 2;   // (warp, pair of lane groups): two lane groups are folded by a shuffle first
 static_assert(kQPlanes * 64 >= kQWarps * kD, "the epilogue reuses the score planes as [warp][G][128] floats");
 
-struct QSparse {
-    const unsigned long long* bmp;
-    const int* tile_off;
-    const __half* scales;
-    const __half* zeros;
-    const unsigned* packed;
-    int64_t bmp_hs, meta_hs;
-    long long packed_words;
-};
-
 struct QDecodeParams {
     QSparse k, v;
     const __half* q;
@@ -59,14 +50,6 @@ __device__ __forceinline__ void cp_async4(void* dst_smem, const void* src) {
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
-template <int BITS>
-struct QBuf {   // one staged tensor of one 64-token block
-    static constexpr int WPT = 64 * BITS / 32;   // words per tile slot
-    uint2 bm[128];
-    unsigned sz[128 * 2];                        // (scale | zero << 16) per group
-    unsigned words[128 * WPT + 4];
-};
 
 // One tile step over quantised codes.  The dequantised value (code - zero) * scale is never
 // materialised: per tile the lane folds the scale into the G coefficients (sc[g] = scale * coef[g])
@@ -483,15 +466,21 @@ extern "C" int mfar_decode_attention_quant(
     const int32_t* k_packed, int64_t k_packed_words,
     const int64_t* v_bitmaps, const int32_t* v_tile_offsets, const void* v_scales, const void* v_zeros,
     const int32_t* v_packed, int64_t v_packed_words,
-    int64_t bmp_head_stride, int64_t meta_head_stride, int n_tokens, int bits, int qgroup,
+    int64_t bmp_head_stride, int64_t meta_head_stride, int n_tokens, const int32_t* n_tokens_dev, int bits, int qgroup,
     const void* k_window, const void* v_window, int64_t win_head_stride, int64_t win_token_stride, int window,
-    float softmax_scale, void* out, int64_t out_stride, void* workspace, size_t workspace_bytes, int nsplit,
-    uint32_t* dev_status, void* stream) {
+    const int32_t* window_len_dev, float softmax_scale, void* out, int64_t out_stride, void* workspace,
+    size_t workspace_bytes, int nsplit, uint32_t* dev_status, void* stream) {
     if (n_kv_heads <= 0 || group <= 0 || n_tokens < 0 || (n_tokens % 64) || window < 0) return MFAR_ERR_ARG;
     if (n_tokens == 0 && window == 0) return MFAR_ERR_ARG;
+    if (group != 1 && group != 2 && group != 4 && group != 8) return MFAR_ERR_ARG;
     if (!q || !out || !workspace) return MFAR_ERR_ARG;
-    QDecodeParams p{};
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if ((reinterpret_cast<uintptr_t>(q) & 3) || (q_stride & 1)) return MFAR_ERR_ALIGN;
+    if (window > 0 && (!k_window || !v_window)) return MFAR_ERR_ARG;
+    if (window > 0 && ((reinterpret_cast<uintptr_t>(k_window) & 15) || (reinterpret_cast<uintptr_t>(v_window) & 15) ||
+                       (win_head_stride & 7) || (win_token_stride & 7)))
+        return MFAR_ERR_ALIGN;
+    if ((bits != 2 && bits != 4) || (qgroup != 32 && qgroup != 64)) return MFAR_ERR_ARG;
+    DecodeParams p{};
     int r;
     if (n_tokens > 0) {
         r = check_q(k_bitmaps, k_tile_offsets, k_scales, k_zeros, k_packed, bits, qgroup);
@@ -504,26 +493,31 @@ extern "C" int mfar_decode_attention_quant(
     p.nrec = p.nsplit + (window > 0 ? 1 : 0);
     const size_t need = counters_bytes(n_kv_heads) + static_cast<size_t>(n_kv_heads) * p.nrec * group * kPartialStride * sizeof(float);
     if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15)) return MFAR_ERR_WORKSPACE;
-    p.ws = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + counters_bytes(n_kv_heads));
+    p.kq = QSparse{reinterpret_cast<const unsigned long long*>(k_bitmaps), k_tile_offsets,
+                   static_cast<const __half*>(k_scales), static_cast<const __half*>(k_zeros),
+                   reinterpret_cast<const unsigned*>(k_packed), bmp_head_stride, meta_head_stride, k_packed_words};
+    p.vq = QSparse{reinterpret_cast<const unsigned long long*>(v_bitmaps), v_tile_offsets,
+                   static_cast<const __half*>(v_scales), static_cast<const __half*>(v_zeros),
+                   reinterpret_cast<const unsigned*>(v_packed), bmp_head_stride, meta_head_stride, v_packed_words};
+    p.q = static_cast<const __half*>(q);
+    p.q_stride = q_stride;
+    p.kwin = static_cast<const __half*>(k_window);
+    p.vwin = static_cast<const __half*>(v_window);
+    p.win_hs = win_head_stride;
+    p.win_ts = win_token_stride;
+    p.W = window;
+    p.W_dev = window_len_dev;
+    p.L_dev = n_tokens_dev;
+    p.cap = 8;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    p.counters = n_kv_heads <= kMaxCountedHeads ? static_cast<unsigned*>(workspace) : nullptr;
+    p.ws = reinterpret_cast<float*>(static_cast<unsigned char*>(workspace) + counters_bytes(n_kv_heads));
+    p.out = static_cast<__half*>(out);
+    p.out_stride = out_stride;
     p.dev_status = dev_status;
-    if (n_tokens > 0) {
-        p.k = QSparse{reinterpret_cast<const unsigned long long*>(k_bitmaps), k_tile_offsets,
-                      static_cast<const __half*>(k_scales), static_cast<const __half*>(k_zeros),
-                      reinterpret_cast<const unsigned*>(k_packed), bmp_head_stride, meta_head_stride, k_packed_words};
-        p.v = QSparse{reinterpret_cast<const unsigned long long*>(v_bitmaps), v_tile_offsets,
-                      static_cast<const __half*>(v_scales), static_cast<const __half*>(v_zeros),
-                      reinterpret_cast<const unsigned*>(v_packed), bmp_head_stride, meta_head_stride, v_packed_words};
-        p.q = static_cast<const __half*>(q);
-        p.q_stride = q_stride;
-        p.group32 = qgroup == 32;
-        r = dispatch_q<MODE_ATTN>(p, group, bits, n_kv_heads, s);
-        if (r) return r;
-    }
-    if (window > 0) {
-        r = launch_window_record(q, q_stride, n_kv_heads, group, k_window, v_window, win_head_stride, win_token_stride,
-                                 window, nullptr, softmax_scale, p.ws, p.nsplit, dev_status, s, true);
-        if (r) return r;
-    }
-    return launch_combine(p.ws, p.nrec, group == 8 ? 4 : group, 1, out, out_stride, n_kv_heads * group, s);
+    p.rec_group = group;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    r = launch_decode_attn_quant(p, group, bits, qgroup == 32, n_kv_heads, p.nrec, s);
+    if (r || p.counters) return r;
+    return launch_combine(p.ws, p.nrec, group, 1, out, out_stride, n_kv_heads * group, s);
 }

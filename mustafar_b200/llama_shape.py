@@ -81,7 +81,7 @@ class SparseLlama:
         self.s, self.B, self.dev = shape, batch, torch.device(device)
         self.sparsity, self.residual, self.sparse = sparsity, residual, sparse
         # 16: pruned values kept as fp16; 2 or 4: pruned values quantised per tile (the reference's quantised model,
-        # models/llama_mustafar_quant_kernel.py); the quantised cache runs its decode steps eagerly
+        # models/llama_mustafar_quant_kernel.py)
         assert cache_bits in (16, 2, 4) and prune_mode in ("block", "step")
         self.step_prune = prune_mode == "step"
         self.cache_bits, self.quant = cache_bits, sparse and cache_bits != 16
@@ -147,8 +147,9 @@ class SparseLlama:
         # the decode calls of this model write their split records here: a buffer of its own, sized for the full
         # cache, so that captured graphs never see it move and other users of the ops cannot grow it away
         self._decode_ws = None
-        if self.sparse and not self.quant:
+        if self.sparse:
             _, nbytes = ops.plan(batch * self.hkv, self.max_tokens, self.wcap, self.G)
+            nbytes = max(nbytes, 65536 + batch * self.hkv * (self.max_tokens // 64 + 1) * self.G * 132 * 4)
             self._decode_ws = ops.new_workspace(self.dev, nbytes)
 
     # ------------------------------------------------------------------ pieces
@@ -265,7 +266,14 @@ class SparseLlama:
         for L in self.layers:
             h = step_ops.add_rmsnorm(x, delta, L.n1, eps)
             qkv = F.linear(h, L.wqkv)
-            if dev_state:
+            if dev_state and self.quant:
+                step_ops.rope_append(qkv, self._inv_freq, self._state[0:1], self._state[1:2], self.hq, self.hkv,
+                                     self._qbuf, L.kwin, L.vwin, **pr)
+                att = ops_quant.decode_attention_quant(self._qbuf, L.ks.as_dict(), L.vs.as_dict(), self.max_tokens,
+                                                       L.kwin, L.vwin, self.G, self.cache_bits,
+                                                       n_tokens_dev=self._state[3:4], window_len=self._state[2:3],
+                                                       workspace=self._decode_ws)
+            elif dev_state:
                 step_ops.rope_append(qkv, self._inv_freq, self._state[0:1], self._state[1:2], self.hq, self.hkv,
                                      self._qbuf, L.kwin, L.vwin, **pr)
                 att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin, L.vwin, self.G, stage_halves=self._stage_bound,
@@ -274,7 +282,8 @@ class SparseLlama:
             elif self.quant:
                 step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin, **pr)
                 att = ops_quant.decode_attention_quant(self._qbuf, L.ks.as_dict(), L.vs.as_dict(), self.compressed,
-                                                       L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G, self.cache_bits)
+                                                       L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G, self.cache_bits,
+                                                       workspace=self._decode_ws)
             else:
                 step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin, **pr)
                 att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G,
@@ -345,7 +354,7 @@ class SparseLlama:
         length and compressed length live in a device tensor that the captured kernels read, so appending a block
         needs no new capture.  Under tensor parallelism the step is a chain of graphs with the NCCL all-reduces
         launched between them."""
-        if not (graph and self.sparse and not self.quant):
+        if not (graph and self.sparse):
             out = self._step_body(token, False)
             self._advance()
             return out

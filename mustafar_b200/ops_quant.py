@@ -15,7 +15,7 @@ import torch
 
 from . import _lib
 from .compression import D, _stream
-from .ops import _debug_check, _dev_status, _workspace, check_device_status, plan
+from .ops import _debug_check, _dev_status, _take_workspace, _workspace, check_device_status, plan
 
 
 def _check(bmp, NZ_quant, tile_offsets, scales, zeros, B):
@@ -128,14 +128,21 @@ mustafar_quant_sparse_value_forward_decode_n1 = mustafar_value_formulation_quant
 
 
 def decode_attention_quant(q, kq: dict, vq: dict, n_tokens: int, k_window, v_window, group: int, bits: int = 2,
-                           softmax_scale: float | None = None, nsplit: int = 0):
+                           softmax_scale: float | None = None, nsplit: int = 0, out: torch.Tensor | None = None,
+                           n_tokens_dev: torch.Tensor | None = None, window_len: torch.Tensor | None = None,
+                           workspace: torch.Tensor | None = None):
     """Fused decode attention over two quantised tensors (dicts as returned by
-    ``compression_quant.compress_quant``) plus the dense fp16 window."""
+    ``compression_quant.compress_quant`` or ``QuantStore.as_dict``) plus the dense fp16 window, one launch.
+    Dequantised values are ``fp16((code - zero) * scale)`` as in the reference's kernels.
+    ``n_tokens_dev`` / ``window_len``: optional CUDA int32 tensors [1] with the current compressed length (then
+    ``n_tokens`` is its upper bound and sizes the launch) / window length (the window tensors give the capacity),
+    so that a captured launch can be replayed while the cache grows; ``workspace`` as in ``ops.decode_attention``."""
     n_kv = kq["bitmaps"].shape[0]
     tiles = 2 * n_tokens
     if q.shape != (n_kv * group, D) or q.dtype != torch.float16 or not q.is_cuda:
         raise RuntimeError("q must be CUDA float16 [n_kv_heads*group, 128]")
-    q = q if q.stride(1) == 1 else q.contiguous()
+    if q.stride(1) != 1 or q.stride(0) % 2 or q.data_ptr() % 4:
+        q = q.contiguous()
     W, kw, vw, wh, wt = 0, None, None, 0, 0
     if k_window is not None and k_window.shape[1] > 0:
         if k_window.stride() != v_window.stride() or k_window.stride(2) != 1:
@@ -144,8 +151,12 @@ def decode_attention_quant(q, kq: dict, vq: dict, n_tokens: int, k_window, v_win
         wh, wt = k_window.stride(0), k_window.stride(1)
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(D)
-    out = torch.empty((n_kv * group, D), dtype=torch.float16, device=q.device)
-    ws = _workspace(q.device, 65536 + n_kv * (max(1, n_tokens // 64) + 1) * group * 132 * 4)
+    if out is None:
+        out = torch.empty((n_kv * group, D), dtype=torch.float16, device=q.device)
+    ws = _take_workspace(workspace, q.device, 65536 + n_kv * (max(1, n_tokens // 64) + 1) * group * 132 * 4)
+    for t, name in ((n_tokens_dev, "n_tokens_dev"), (window_len, "window_len")):
+        if t is not None and (not t.is_cuda or t.dtype != torch.int32 or t.numel() != 1):
+            raise RuntimeError(f"{name} must be a CUDA int32 tensor with one element")
     st = _dev_status(q.device)
     # compact tensors hold exactly `tiles` tiles per head; an arena (QuantStore.as_dict) says how far apart heads are
     hs = int(kq.get("head_stride", tiles))
@@ -158,7 +169,8 @@ def decode_attention_quant(q, kq: dict, vq: dict, n_tokens: int, k_window, v_win
         kq["packed"].data_ptr(), kq["packed"].numel(),
         vq["bitmaps"].data_ptr(), vq["tile_offsets"].data_ptr(), vq["scales"].data_ptr(), vq["zeros"].data_ptr(),
         vq["packed"].data_ptr(), vq["packed"].numel(),
-        hs, hs, n_tokens, bits, qg, kw, vw, wh, wt, W, float(softmax_scale), out.data_ptr(), out.stride(0),
+        hs, hs, n_tokens, None if n_tokens_dev is None else n_tokens_dev.data_ptr(), bits, qg, kw, vw, wh, wt, W,
+        None if window_len is None else window_len.data_ptr(), float(softmax_scale), out.data_ptr(), out.stride(0),
         ws.data_ptr(), ws.numel(), nsplit, st.data_ptr(), _stream())
     _lib.check(r, "mfar_decode_attention_quant")
     if _debug_check():
