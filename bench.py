@@ -49,6 +49,9 @@ def parse():
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="budget of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--parity-heads", type=int, default=4, help="kv heads checked against the CPU oracle after timing")
+    ap.add_argument("--no-e2e-llama", action="store_true",
+                    help="skip the end-to-end Llama-3-8B-shape generation reported under \"e2e_llama\"")
+    ap.add_argument("--e2e-llama-new", type=int, default=256, help="generated tokens of the end-to-end run")
     return ap.parse_args()
 
 
@@ -326,6 +329,18 @@ def main():
     from mustafar_b200.sharding import max_over_ranks
     total_ms, e2e_ms, per_launch_ms = (max_over_ranks(x, dist, dev) for x in (total_ms, e2e_ms, per_launch_ms))
 
+    # second half of the metric: Llama-3-8B-shape decode tokens/s, end to end (random-init weights, prompt 4096, greedy
+    # steps at batch 32 per GPU, batch-sharded at every N; with 8 GPUs also the 8-way head-tensor-parallel arm, whose
+    # all-reduces after o_proj / down_proj are the only collectives of this benchmark)
+    e2e_llama = None
+    if not a.no_e2e_llama:
+        from mustafar_b200.e2e_llama import run_e2e
+        del ks, vs, kw, vw, ws
+        torch.cuda.empty_cache()
+        e2e_llama = {"batch_sharded": run_e2e(dev, rank, world, dist, new=a.e2e_llama_new, parallel="dp")}
+        if world == 8:
+            e2e_llama["tensor_parallel"] = run_e2e(dev, rank, world, dist, new=a.e2e_llama_new, parallel="tp")
+
     if rank == 0:
         peak, which = measured_peak_gbs()
         achieved = alg_bytes / (per_launch_ms * 1e-3) / 1e9
@@ -341,6 +356,7 @@ def main():
             "step_ms": {"min": step_ms[0], "median": step_ms[len(step_ms) // 2], "max": step_ms[-1]},
             "gpu_launches": a.steps,
             "parity_check": parity,
+            "e2e_llama": e2e_llama,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": which, "frac_of_nominal_8000": achieved / 8000.0,
                          "algorithmic_bytes_per_launch": alg_bytes,

@@ -60,7 +60,10 @@ const char* mfar_status_string(int status);
  *           keep |x| >= thr (ties kept).  prune_rank = 0: input is taken as is.
  *
  * x            device, fp16, element (h, t, c) at x[h*x_head_stride + t*x_token_stride + c];
- *              strides in elements, multiples of 8; x 16-byte aligned.
+ *              strides in elements, multiples of 8; x 16-byte aligned.  heads_per_group > 0
+ *              addresses a two-level layout instead: head h = (g, j), g = h / heads_per_group,
+ *              at x[g*x_group_stride + j*x_head_stride + ...] - e.g. the [batch, token, kv head, 128]
+ *              output of a fused q|k|v projection read in place (group = sequence).
  * n_tokens     multiple of 64.  Tiles are appended at tile index tile_start
  *              (= tokens already in the cache * 2); tile_start = 0 starts a cache.
  * bitmaps      device int64, head h at bitmaps + h*bmp_head_stride.
@@ -85,6 +88,7 @@ const char* mfar_status_string(int status);
 size_t mfar_compress_scratch_bytes(int n_heads, int n_tokens);
 
 int mfar_compress_fp16(const void* x, int64_t x_head_stride, int64_t x_token_stride,
+                       int heads_per_group, int64_t x_group_stride,
                        int n_heads, int n_tokens, int kind, int prune_rank,
                        int64_t* bitmaps, int64_t bmp_head_stride,
                        int32_t* accum, int64_t acc_head_stride, int64_t tile_start,
@@ -124,7 +128,7 @@ int mfar_prune_fp16(const void* x, void* y, int64_t n_rows, int64_t row_stride,
  * fp32, stored fp16; codes from the stored fp16 parameters with IEEE division).  bits = 4 and
  * group = 32 (a fresh scale/zero every 32 nonzeros of a tile) have no reference counterpart.
  *
- * x, strides, n_tokens, kind, prune_rank, bitmaps, tile_start: as mfar_compress_fp16.
+ * x, strides, heads_per_group, n_tokens, kind, prune_rank, bitmaps, tile_start: as mfar_compress_fp16.
  * tile_offsets/counts/units  device int32, head h at + h*meta_head_stride (counts, units may be NULL);
  *              tile_offsets[t] = uint32 offset of tile t in the flat `packed` buffer.
  * scales/zeros device fp16, (64/group) entries per tile: index (h*meta_head_stride + t)*(64/group) + g.
@@ -136,7 +140,8 @@ int mfar_prune_fp16(const void* x, void* y, int64_t n_rows, int64_t row_stride,
  *              head_tail[h] (required) = words already used, updated by the call.
  * scratch      mfar_compress_scratch_bytes() bytes, cleared by the call.
  * ------------------------------------------------------------------------- */
-int mfar_compress_quant(const void* x, int64_t x_head_stride, int64_t x_token_stride, int n_heads,
+int mfar_compress_quant(const void* x, int64_t x_head_stride, int64_t x_token_stride,
+                        int heads_per_group, int64_t x_group_stride, int n_heads,
                         int n_tokens, int kind, int prune_rank, int bits, int group,
                         int64_t* bitmaps, int64_t bmp_head_stride, int32_t* tile_offsets,
                         int32_t* counts, int32_t* units, void* scales, void* zeros,

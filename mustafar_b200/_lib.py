@@ -21,12 +21,12 @@ SIGNATURES = {
     "mfar_version": (_i32, []),
     "mfar_status_string": (C.c_char_p, [_i32]),
     "mfar_compress_scratch_bytes": (_sz, [_i32, _i32]),
-    "mfar_compress_fp16": (_i32, [_vp, _i64, _i64, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _i64,
+    "mfar_compress_fp16": (_i32, [_vp, _i64, _i64, _i32, _i64, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _i64,
                                   _vp, _vp, _i64, _i64, _vp, _sz, _vp, _vp, _vp]),
     "mfar_compress_fp16_noalloc": (_i32, [_vp, _i64, _i64, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _i64,
                                           _vp, _vp, _i64, _i64, _vp, _vp, _vp]),
     "mfar_prune_fp16": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),
-    "mfar_compress_quant": (_i32, [_vp, _i64, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp,
+    "mfar_compress_quant": (_i32, [_vp, _i64, _i64, _i32, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp,
                                    _i64, _i64, _vp, _i64, _i64, _vp, _vp, _sz, _vp, _vp]),
     "mfar_decode_plan": (_i32, [_i32, _i32, _i32, _i32, C.POINTER(_i32), C.POINTER(_sz), _i32]),
     "mfar_decode_attention_fp16": (_i32, [_vp, _i64, _i32, _i32,

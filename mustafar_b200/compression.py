@@ -28,17 +28,27 @@ def _stream() -> int:
 
 
 def _check_input(x: torch.Tensor) -> torch.Tensor:
+    """[heads, tokens, 128], or [groups, heads per group, tokens, 128] (any strides that are multiples of 8 with a
+    unit channel stride, e.g. the [batch, token, kv head, 128] projection output viewed as [batch, kv head, token, 128]):
+    read in place; anything else is made contiguous first."""
     if not x.is_cuda:
         raise RuntimeError("mustafar_b200: input must be a CUDA tensor (there is no CPU path)")
-    if x.dim() != 3 or x.shape[2] != D:
-        raise RuntimeError(f"expected [heads, tokens, {D}], got {tuple(x.shape)}")
+    if x.dim() not in (3, 4) or x.shape[-1] != D:
+        raise RuntimeError(f"expected [heads, tokens, {D}] or [groups, heads, tokens, {D}], got {tuple(x.shape)}")
     if x.dtype != torch.float16:
         raise RuntimeError("expected float16")
-    if x.shape[1] % 64 != 0:
+    if x.shape[-2] % 64 != 0:
         raise RuntimeError("token count must be a multiple of 64")
-    if x.stride(2) != 1 or x.stride(1) % 8 or x.stride(0) % 8 or x.data_ptr() % 16:
+    if x.stride(-1) != 1 or any(st % 8 for st in x.stride()[:-1]) or x.data_ptr() % 16:
         x = x.contiguous()
     return x
+
+
+def _source_args(x: torch.Tensor):
+    """(pointer, head stride, token stride, heads per group, group stride, heads, tokens) of a checked input."""
+    if x.dim() == 3:
+        return x.data_ptr(), x.stride(0), x.stride(1), 0, 0, x.shape[0], x.shape[1]
+    return x.data_ptr(), x.stride(1), x.stride(2), x.shape[1], x.stride(0), x.shape[0] * x.shape[1], x.shape[2]
 
 
 def prune(x: torch.Tensor, sparsity: float, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -85,11 +95,11 @@ class SparseStore:
         return self._scratch
 
     def append(self, x: torch.Tensor, prune_rank: int = 0) -> None:
-        """Compress ``x`` [n_heads, n, 128] (n % 64 == 0) behind the tokens already stored.
-        ``prune_rank`` > 0 fuses the magnitude prune (see ``keep_rank``)."""
+        """Compress ``x`` [n_heads, n, 128] or [groups, heads per group, n, 128] (n % 64 == 0; strided views are read
+        in place) behind the tokens already stored.  ``prune_rank`` > 0 fuses the magnitude prune (see ``keep_rank``)."""
         x = _check_input(x)
-        n = x.shape[1]
-        if x.shape[0] != self.n_heads:
+        ptr, hs, ts, hpg, gs, heads, n = _source_args(x)
+        if heads != self.n_heads:
             raise RuntimeError("head count mismatch")
         if self.tokens + n > self.max_tokens:
             raise RuntimeError("SparseStore is full")
@@ -97,7 +107,7 @@ class SparseStore:
             return
         scratch = self._scratch_for(n)
         st = _lib.lib().mfar_compress_fp16(
-            x.data_ptr(), x.stride(0), x.stride(1), self.n_heads, n, self.kind, prune_rank,
+            ptr, hs, ts, hpg, gs, self.n_heads, n, self.kind, prune_rank,
             self.bitmaps.data_ptr(), self.tiles_cap, self.accum.data_ptr(), self.tiles_cap + 1, 2 * self.tokens,
             self.nz.data_ptr(), None, self.nz_capacity, self.nz_capacity,
             scratch.data_ptr(), scratch.numel(), self.stats.data_ptr(), self.stats.data_ptr() + 4, _stream())
@@ -129,6 +139,8 @@ class SparseStore:
 
 def _convert(inputs: torch.Tensor, kind: int):
     x = _check_input(inputs)
+    if x.dim() != 3:
+        raise RuntimeError(f"expected [heads, tokens, {D}], got {tuple(x.shape)}")
     Bh, L, _ = x.shape
     store = SparseStore(Bh, max(L, 64), kind, x.device)
     if L:

@@ -10,13 +10,15 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .compression import D, KEY, VALUE, _check_input, _stream
+from .compression import D, KEY, VALUE, _check_input, _source_args, _stream
 
 
 def compress_quant(x: torch.Tensor, kind: int, prune_rank: int = 0, bits: int = 2, group: int = 64):
     """Returns dict(bitmaps, tile_offsets, packed, counts, units, scales, zeros) in the reference's
     compact layout (one flat int32 code buffer shared by all heads)."""
     x = _check_input(x)
+    if x.dim() != 3:
+        raise RuntimeError("compress_quant expects [heads, tokens, 128]")
     Bh, L, _ = x.shape
     T = 2 * L
     ngrp = 64 // group
@@ -35,7 +37,7 @@ def compress_quant(x: torch.Tensor, kind: int, prune_rank: int = 0, bits: int = 
         need = _lib.lib().mfar_compress_scratch_bytes(Bh, L)
         scratch = torch.empty(need, dtype=torch.uint8, device=dev)
         st = _lib.lib().mfar_compress_quant(
-            x.data_ptr(), x.stride(0), x.stride(1), Bh, L, kind, prune_rank, bits, group,
+            x.data_ptr(), x.stride(0), x.stride(1), 0, 0, Bh, L, kind, prune_rank, bits, group,
             bitmaps.data_ptr(), T, tile_offsets.data_ptr(), counts.data_ptr(), units.data_ptr(),
             scales.data_ptr(), zeros.data_ptr(), T, 0, packed.data_ptr(), 0, worst, info.data_ptr(),
             scratch.data_ptr(), need, info.data_ptr() + 4 * Bh, _stream())
@@ -77,10 +79,11 @@ class QuantStore:
         self._scratch = None
 
     def append(self, x: torch.Tensor, prune_rank: int = 0) -> None:
-        """Prune (``prune_rank`` > 0), quantise and store ``x`` [n_heads, n, 128], n % 64 == 0, behind the tokens held."""
+        """Prune (``prune_rank`` > 0), quantise and store ``x`` [n_heads, n, 128] or [groups, heads per group, n, 128]
+        (n % 64 == 0, strided views read in place) behind the tokens held."""
         x = _check_input(x)
-        n = x.shape[1]
-        if x.shape[0] != self.n_heads:
+        ptr, hs, ts, hpg, gs, heads, n = _source_args(x)
+        if heads != self.n_heads:
             raise RuntimeError("head count mismatch")
         if self.tokens + n > self.max_tokens:
             raise RuntimeError("QuantStore is full")
@@ -91,7 +94,7 @@ class QuantStore:
             self._scratch = torch.empty(need, dtype=torch.uint8, device=self.bitmaps.device)
         T = self.tiles_cap
         st = _lib.lib().mfar_compress_quant(
-            x.data_ptr(), x.stride(0), x.stride(1), self.n_heads, n, self.kind, prune_rank, self.bits, self.group,
+            ptr, hs, ts, hpg, gs, self.n_heads, n, self.kind, prune_rank, self.bits, self.group,
             self.bitmaps.data_ptr(), T, self.tile_offsets.data_ptr(), self.counts.data_ptr(), self.units.data_ptr(),
             self.scales.data_ptr(), self.zeros.data_ptr(), T, 2 * self.tokens, self.packed.data_ptr(),
             self.words_capacity, self.words_capacity, self.head_tail.data_ptr(),

@@ -26,6 +26,8 @@ namespace mfar {
 struct CompressParams {
     const __half* x;
     int64_t xhs, xts;
+    int hpg;                       // heads per group (0: one stride for all heads)
+    int64_t xgs;                   // stride between groups of heads
     int n_heads, nblk, rank;
     unsigned long long* bmp;
     int64_t bmp_hs;
@@ -69,7 +71,7 @@ __global__ void __launch_bounds__(128, MFAR_COMPRESS_MIN_CTAS) compress_kernel(C
         // threshold and ends up with one flag per element: kept and nonzero
         uint4 v[8];
         {
-            const uint4* src = reinterpret_cast<const uint4*>(p.x + h * p.xhs + (static_cast<int64_t>(b) * 64 + r) * p.xts);
+            const uint4* src = reinterpret_cast<const uint4*>(p.x + (p.hpg > 0 ? (h / p.hpg) * p.xgs + (h % p.hpg) * p.xhs : h * p.xhs) + (static_cast<int64_t>(b) * 64 + r) * p.xts);
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = ldg_nc_u4(src + 2 * j + hh);
         }
@@ -246,6 +248,7 @@ extern "C" size_t mfar_compress_scratch_bytes(int n_heads, int n_tokens) {
 }
 
 extern "C" int mfar_compress_fp16(const void* x, int64_t x_head_stride, int64_t x_token_stride,
+                                  int heads_per_group, int64_t x_group_stride,
                                   int n_heads, int n_tokens, int kind, int prune_rank,
                                   int64_t* bitmaps, int64_t bmp_head_stride,
                                   int32_t* accum, int64_t acc_head_stride, int64_t tile_start,
@@ -257,6 +260,7 @@ extern "C" int mfar_compress_fp16(const void* x, int64_t x_head_stride, int64_t 
     if (prune_rank < 0 || prune_rank > kD || tile_start < 0 || (tile_start % kTilesPerBlock) != 0) return MFAR_ERR_ARG;
     if (n_heads == 0 || n_tokens == 0) return MFAR_OK;
     if (!x || !bitmaps || !accum || !nz || !scratch) return MFAR_ERR_ARG;
+    if (heads_per_group > 0 && (x_group_stride & 7)) return MFAR_ERR_ALIGN;
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (x_head_stride & 7) || (x_token_stride & 7) ||
         (reinterpret_cast<uintptr_t>(nz) & 15) || (nz_head_stride & 7) ||
         (reinterpret_cast<uintptr_t>(scratch) & 15) || (reinterpret_cast<uintptr_t>(bitmaps) & 7) ||
@@ -274,6 +278,8 @@ extern "C" int mfar_compress_fp16(const void* x, int64_t x_head_stride, int64_t 
     p.x = static_cast<const __half*>(x);
     p.xhs = x_head_stride;
     p.xts = x_token_stride;
+    p.hpg = heads_per_group > 0 ? heads_per_group : 0;
+    p.xgs = x_group_stride;
     p.n_heads = n_heads;
     p.nblk = nblk;
     p.rank = prune_rank;
@@ -354,7 +360,7 @@ extern "C" int mfar_compress_fp16_noalloc(const void* x, int64_t x_head_stride, 
         if (cudaGetSymbolAddress(&addr, g_static_scratch) != cudaSuccess || addr == nullptr) return MFAR_ERR_LAUNCH;
         g_static_scratch_addr[dev] = addr;
     }
-    return mfar_compress_fp16(x, x_head_stride, x_token_stride, n_heads, n_tokens, kind, prune_rank, bitmaps,
+    return mfar_compress_fp16(x, x_head_stride, x_token_stride, 0, 0, n_heads, n_tokens, kind, prune_rank, bitmaps,
                               bmp_head_stride, accum, acc_head_stride, tile_start, nz, nz_offset, nz_head_stride,
                               nz_capacity, g_static_scratch_addr[dev], kStaticScratchBytes, dev_status,
                               max_block_halves, stream);

@@ -20,6 +20,8 @@ namespace mfar {
 struct QuantParams {
     const __half* x;
     int64_t xhs, xts;
+    int hpg;                       // heads per group (0: one stride for all heads)
+    int64_t xgs;                   // stride between groups of heads
     int n_heads, nblk, rank, bits, group;
     unsigned long long* bmp;
     int* tile_off;
@@ -86,7 +88,7 @@ __global__ void __launch_bounds__(128) compress_quant_kernel(QuantParams p) {
     // ---- the pair loads one row, selects the threshold, ends up with one "kept and nonzero" flag per element
     uint4 v[8];
     {
-        const uint4* src = reinterpret_cast<const uint4*>(p.x + h * p.xhs + (static_cast<int64_t>(b) * 64 + r) * p.xts);
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + (p.hpg > 0 ? (h / p.hpg) * p.xgs + (h % p.hpg) * p.xhs : h * p.xhs) + (static_cast<int64_t>(b) * 64 + r) * p.xts);
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = ldg_nc_u4(src + 2 * j + hh);
     }
@@ -298,7 +300,8 @@ __global__ void quant_bump_tails(const unsigned long long* state, int nblk, int 
 
 using namespace mfar;
 
-extern "C" int mfar_compress_quant(const void* x, int64_t x_head_stride, int64_t x_token_stride, int n_heads,
+extern "C" int mfar_compress_quant(const void* x, int64_t x_head_stride, int64_t x_token_stride,
+                                   int heads_per_group, int64_t x_group_stride, int n_heads,
                                    int n_tokens, int kind, int prune_rank, int bits, int group,
                                    int64_t* bitmaps, int64_t bmp_head_stride, int32_t* tile_offsets,
                                    int32_t* counts, int32_t* units, void* scales, void* zeros,
@@ -312,6 +315,7 @@ extern "C" int mfar_compress_quant(const void* x, int64_t x_head_stride, int64_t
     if (packed_head_stride < 0 || (packed_head_stride > 0 && !head_tail)) return MFAR_ERR_ARG;
     if (n_heads == 0 || n_tokens == 0) return MFAR_OK;
     if (!x || !bitmaps || !tile_offsets || !scales || !zeros || !packed || !scratch) return MFAR_ERR_ARG;
+    if (heads_per_group > 0 && (x_group_stride & 7)) return MFAR_ERR_ALIGN;
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (x_head_stride & 7) || (x_token_stride & 7) ||
         (reinterpret_cast<uintptr_t>(scratch) & 15) || (reinterpret_cast<uintptr_t>(packed) & 3))
         return MFAR_ERR_ALIGN;
@@ -327,6 +331,8 @@ extern "C" int mfar_compress_quant(const void* x, int64_t x_head_stride, int64_t
     p.x = static_cast<const __half*>(x);
     p.xhs = x_head_stride;
     p.xts = x_token_stride;
+    p.hpg = heads_per_group > 0 ? heads_per_group : 0;
+    p.xgs = x_group_stride;
     p.n_heads = n_heads;
     p.nblk = nblk;
     p.rank = prune_rank;

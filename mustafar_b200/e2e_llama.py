@@ -21,33 +21,18 @@ from .llama_shape import LlamaShape, SparseLlama
 from .sharding import max_over_ranks
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--batch", type=int, default=32)
-    ap.add_argument("--prompt", type=int, default=4096)
-    ap.add_argument("--new", type=int, default=256)
-    ap.add_argument("--parallel", default="dp", choices=["tp", "dp"])
-    ap.add_argument("--sparsity", type=float, default=0.7)
-    ap.add_argument("--layers", type=int, default=32)
-    ap.add_argument("--no-graph", action="store_true", help="launch every decode step eagerly instead of replaying a CUDA graph")
-    ap.add_argument("--dense", action="store_true", help="dense pruned cache + torch attention (comparison arm)")
-    ap.add_argument("--bits", type=int, default=16, choices=[16, 4, 2],
-                    help="16: pruned values kept as fp16; 4 / 2: quantised per tile (decode steps run eagerly)")
-    a = ap.parse_args()
-    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
-    tp = world if a.parallel == "tp" else 1
-    shape = LlamaShape(n_layers=a.layers)
-    model = SparseLlama(shape, a.batch, a.prompt + a.new, dev, sparsity=a.sparsity, seed=1234,
-                        tp_rank=rank if tp > 1 else 0, tp_world=tp, dist=dist, sparse=not a.dense, cache_bits=a.bits)
+def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 4096, new: int = 256,
+            parallel: str = "dp", sparsity: float = 0.7, layers: int = 32, graph: bool = True, dense: bool = False,
+            bits: int = 16, prune_mode: str = "block") -> dict:
+    """One generation (prefill + ``new`` greedy steps) on this rank's GPU; returns the result record (the same on
+    every rank: times are the maximum over ranks).  ``dist``: an initialised torch.distributed module or None."""
+    tp = world if parallel == "tp" else 1
+    shape = LlamaShape(n_layers=layers)
+    model = SparseLlama(shape, batch, prompt + new, dev, sparsity=sparsity, seed=1234,
+                        tp_rank=rank if tp > 1 else 0, tp_world=tp, dist=dist, sparse=not dense, cache_bits=bits,
+                        prune_mode=prune_mode)
     g = torch.Generator(device=dev).manual_seed(99 if tp > 1 else 99 + rank)
-    toks = torch.randint(0, shape.vocab, (a.batch, a.prompt), generator=g, device=dev)
+    toks = torch.randint(0, shape.vocab, (batch, prompt), generator=g, device=dev)
 
     def sync():
         torch.cuda.synchronize()
@@ -61,42 +46,77 @@ def main():
     nxt = model.prefill(toks).argmax(-1)
     e[1].record()
     marks = []
-    for _ in range(a.new - 1):
-        nxt = model.decode_step(nxt, graph=not a.no_graph).argmax(-1)
+    for _ in range(new - 1):
+        nxt = model.decode_step(nxt, graph=graph).argmax(-1)
         marks.append(torch.cuda.Event(enable_timing=True))
         marks[-1].record()
     e[2].record()
     torch.cuda.synchronize()
-    # per-step device time: the median leaves out the steps that append a block or re-capture the graph
+    # per-step device time: the median leaves out the steps that append a block or capture the graph
     gaps = sorted(x.elapsed_time(y) for x, y in zip(marks[:-1], marks[1:]))
     steady_ms = max_over_ranks(gaps[len(gaps) // 2], dist, dev) if gaps else 0.0
     slowest_ms = max_over_ranks(gaps[-1], dist, dev) if gaps else 0.0
     prefill_ms = max_over_ranks(e[0].elapsed_time(e[1]), dist, dev)
     decode_ms = max_over_ranks(e[1].elapsed_time(e[2]), dist, dev)
-    seqs = a.batch * (1 if tp > 1 else world)
+    compress_ms = max_over_ranks(model.prefill_compress_ms, dist, dev)
+    seqs = batch * (1 if tp > 1 else world)
     # bytes the compressed part of the cache takes per (token, kv head), K + V, measured on the first layer of this rank
     cache_bytes = None
-    if not a.dense and model.compressed:
+    if not dense and model.compressed:
         L0 = model.layers[0]
         per = 0.0
         for st in (L0.ks, L0.vs):
             tiles = 2 * model.compressed
-            if a.bits == 16:
+            if bits == 16:
                 per += 8 * tiles + 4 * (tiles + 1) + 2.0 * float(st.packed_lengths().float().mean())
             else:
                 per += (8 + 4 + 2 + 2) * tiles + 4.0 * float(st.head_tail.float().mean())
         cache_bytes = per / model.compressed
+    del model
+    torch.cuda.empty_cache()
+    return {
+        "metric": "llama3_8b_shape_decode_throughput", "unit": "tok/s", "n_gpus": world,
+        "value": seqs * (new - 1) / (decode_ms * 1e-3), "tpot_ms": decode_ms / (new - 1), "tpot_median_ms": steady_ms,
+        "slowest_step_ms": slowest_ms, "ttft_ms": prefill_ms, "ttft_compression_ms": compress_ms,
+        "compressed_cache_bytes_per_token_per_kv_head": cache_bytes, "dense_fp16_bytes_per_token_per_kv_head": 512,
+        "config": {"workload": f"Llama-3-8B shape, {layers} layers, prompt {prompt}, {new} new tokens, "
+                               f"batch {batch} per {'job' if tp > 1 else 'GPU'}, sparsity {sparsity}, window 128, "
+                               f"pruning per {prune_mode}",
+                   "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}",
+                   "cache": "dense-pruned torch" if dense else ("sparse fp16" if bits == 16 else f"sparse {bits}-bit"),
+                   "cuda_graph": (False if (not graph or dense) else
+                                  ("one graph per stretch between collectives" if tp > 1 else True))},
+        "data": "synthetic (random-init weights, random prompt ids)", "dtype": "f16"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--prompt", type=int, default=4096)
+    ap.add_argument("--new", type=int, default=256)
+    ap.add_argument("--parallel", default="dp", choices=["tp", "dp"])
+    ap.add_argument("--sparsity", type=float, default=0.7)
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--no-graph", action="store_true", help="launch every decode step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--dense", action="store_true", help="dense pruned cache + torch attention (comparison arm)")
+    ap.add_argument("--bits", type=int, default=16, choices=[16, 4, 2],
+                    help="16: pruned values kept as fp16; 4 / 2: quantised per tile")
+    ap.add_argument("--prune-mode", default="block", choices=["block", "step"],
+                    help="block: prune with the compression, 256 tokens at a time; step: prune the token that leaves "
+                         "the residual window at every decode step")
+    a = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    res = run_e2e(dev, rank, world, dist, a.batch, a.prompt, a.new, a.parallel, a.sparsity, a.layers, not a.no_graph,
+                  a.dense, a.bits, a.prune_mode)
     if rank == 0:
-        print(json.dumps({
-            "metric": "llama3_8b_shape_decode_throughput", "unit": "tok/s", "n_gpus": world,
-            "value": seqs * (a.new - 1) / (decode_ms * 1e-3), "tpot_ms": decode_ms / (a.new - 1), "tpot_median_ms": steady_ms,
-            "slowest_step_ms": slowest_ms, "ttft_ms": prefill_ms,
-            "compressed_cache_bytes_per_token_per_kv_head": cache_bytes, "dense_fp16_bytes_per_token_per_kv_head": 512,
-            "config": {"workload": f"Llama-3-8B shape, {a.layers} layers, prompt {a.prompt}, {a.new} new tokens, "
-                                   f"batch {a.batch} per {'job' if tp > 1 else 'GPU'}, sparsity {a.sparsity}, window 128",
-                       "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}", "cache": "dense-pruned torch" if a.dense else ("sparse fp16" if a.bits == 16 else f"sparse {a.bits}-bit"),
-                       "cuda_graph": (False if (a.no_graph or a.dense or a.bits != 16) else ("one graph per stretch between collectives" if tp > 1 else True))},
-            "data": "synthetic (random-init weights, random prompt ids)", "dtype": "f16"}))
+        print(json.dumps(res))
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

@@ -146,6 +146,7 @@ class SparseLlama:
         self._stage_bound = min(8192, 64 * (kept + 3) + 7 * 128)
         # the decode calls of this model write their split records here: a buffer of its own, sized for the full
         # cache, so that captured graphs never see it move and other users of the ops cannot grow it away
+        self.prefill_compress_ms = self.prefill_attention_ms = 0.0
         self._decode_ws = None
         if self.sparse:
             _, nbytes = ops.plan(batch * self.hkv, self.max_tokens, self.wcap, self.G)
@@ -178,39 +179,69 @@ class SparseLlama:
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
     def prefill(self, tokens: torch.Tensor) -> torch.Tensor:
-        """tokens [B, T] -> logits of the last position [B, vocab]; fills the caches."""
+        """tokens [B, T] -> logits of the last position [B, vocab]; fills the caches.
+
+        The cache work of a layer (prune + compression of the first ``Lc`` tokens, copy of the rest into the dense
+        window) runs on a side stream straight from the projection outputs - K after RoPE, V as the strided
+        [B, T, kv head, 128] view of the fused q|k|v GEMM result, neither is copied or flattened first - while the main
+        stream goes on with this layer's attention and MLP and the next layer's GEMMs (the reference compresses
+        between layers with the GPU otherwise idle, ``models/llama_mustafar_kernel.py:540-560``).  The device time of
+        the cache work and of the dense attention is kept in ``prefill_compress_ms`` / ``prefill_attention_ms``."""
         B, T = tokens.shape
         assert B == self.B and self.tokens == 0 and T <= self.max_tokens + self.residual
         pos = torch.arange(T, device=self.dev)
         Lc = max(0, (T - self.residual) // 256) * 256
         x = self.embed[tokens]
+        main = torch.cuda.current_stream(self.dev)
+        side = torch.cuda.Stream(self.dev) if self.sparse else None
+        marks = []
         for L in self.layers:
             h = _rms(x, L.n1, self.s.rms_eps)
             q, k, v = self._qkv(L, h, pos)
+            if self.sparse:
+                ready = torch.cuda.Event()
+                ready.record(main)
+                with torch.cuda.stream(side):
+                    side.wait_event(ready)
+                    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    c0.record(side)
+                    if Lc:
+                        L.ks.append(k[:, :, :Lc], self.rank_keep)       # strided 4-D views: nothing is copied
+                        L.vs.append(v[:, :, :Lc], self.rank_keep)
+                    L.kwin.view(B, self.hkv, self.wcap, D)[:, :, :T - Lc] = k[:, :, Lc:]
+                    L.vwin.view(B, self.hkv, self.wcap, D)[:, :, :T - Lc] = v[:, :, Lc:]
+                    if self.step_prune and T - Lc > self.residual:      # only the newest `residual` tokens stay dense
+                        n = T - Lc - self.residual
+                        L.kwin[:, :n] = comp.prune(L.kwin[:, :n].contiguous(), self.sparsity)
+                        L.vwin[:, :n] = comp.prune(L.vwin[:, :n].contiguous(), self.sparsity)
+                    c1.record(side)
+                    marks.append(("compress", c0, c1))
+                k.record_stream(side)
+                v.record_stream(side)
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(main)
             att = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            a1.record(main)
+            marks.append(("attention", a0, a1))
             x = x + self._allreduce(F.linear(att.transpose(1, 2).reshape(B, T, self.hq * D), L.wo))
             x = x + self._mlp(L, _rms(x, L.n2, self.s.rms_eps))
-            kf, vf = k.reshape(B * self.hkv, T, D), v.reshape(B * self.hkv, T, D)
-            if self.sparse:
-                if Lc:
-                    L.ks.append(kf[:, :Lc], self.rank_keep)       # strided views: no copy
-                    L.vs.append(vf[:, :Lc], self.rank_keep)
-                L.kwin[:, :T - Lc] = kf[:, Lc:]
-                L.vwin[:, :T - Lc] = vf[:, Lc:]
-                if self.step_prune and T - Lc > self.residual:      # only the newest `residual` tokens stay dense
-                    n = T - Lc - self.residual
-                    L.kwin[:, :n] = comp.prune(L.kwin[:, :n].contiguous(), self.sparsity)
-                    L.vwin[:, :n] = comp.prune(L.vwin[:, :n].contiguous(), self.sparsity)
-            else:
+            if not self.sparse:
+                kf, vf = k.reshape(B * self.hkv, T, D), v.reshape(B * self.hkv, T, D)
                 L.ks[:, :T], L.vs[:, :T] = kf, vf
                 Lp = max(Lc, T - self.residual) if self.step_prune else Lc
                 if Lp > 0:
                     L.ks[:, :Lp] = comp.prune(kf[:, :Lp].contiguous(), self.sparsity)
                     L.vs[:, :Lp] = comp.prune(vf[:, :Lp].contiguous(), self.sparsity)
             del q, k, v, att
+        if side is not None:
+            main.wait_stream(side)
         self.tokens, self.compressed, self.wlen = T, Lc, T - Lc
         self._stage_hint = None
-        return self._logits(x[:, -1])
+        out = self._logits(x[:, -1])
+        torch.cuda.synchronize(self.dev)
+        self.prefill_compress_ms = sum(a.elapsed_time(b) for n, a, b in marks if n == "compress")
+        self.prefill_attention_ms = sum(a.elapsed_time(b) for n, a, b in marks if n == "attention")
+        return out
 
     # ------------------------------------------------------------------ one decode step
     def _hint(self):

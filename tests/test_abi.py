@@ -53,9 +53,9 @@ def test_scratch_and_plan_sizes(lib):
 
 def test_host_argument_validation_needs_no_gpu(lib):
     # null pointers / bad sizes are rejected before any CUDA call
-    assert lib.mfar_compress_fp16(None, 0, 0, 1, 64, 0, 0, None, 0, None, 0, 0, None, None, 0, 0, None, 0,
+    assert lib.mfar_compress_fp16(None, 0, 0, 0, 0, 1, 64, 0, 0, None, 0, None, 0, 0, None, None, 0, 0, None, 0,
                                   None, None, None) == 1
-    assert lib.mfar_compress_fp16(None, 0, 0, 1, 65, 0, 0, None, 0, None, 0, 0, None, None, 0, 0, None, 0,
+    assert lib.mfar_compress_fp16(None, 0, 0, 0, 0, 1, 65, 0, 0, None, 0, None, 0, 0, None, None, 0, 0, None, 0,
                                   None, None, None) == 1
     assert lib.mfar_prune_fp16(None, None, 4, 128, 200, None) == 1
     assert lib.mfar_prune_fp16(None, None, 0, 128, 89, None) == 0          # empty input is fine

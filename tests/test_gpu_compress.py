@@ -180,3 +180,25 @@ def test_wire_format_round_trip_feeds_decode():
     ks2.append(k[:, :64], comp.keep_rank(0.7))
     assert ks2.tokens == L + 64
     ks2.check()
+
+
+@pytest.mark.parametrize("kind", ["key", "value"])
+def test_projection_layout_is_compressed_in_place(kind):
+    """A [batch, token, kv head, 128] slice of a fused q|k|v projection output, viewed as [batch, kv head, token, 128]
+    (what the prefill hands over for V), is read through its strides: same cache as for the flattened copy."""
+    from mustafar_b200 import compression as comp
+    B, T, hq, hkv = 3, 320, 8, 2
+    g = torch.Generator(device="cuda").manual_seed(12)
+    qkv = torch.randn(B, T, (hq + 2 * hkv) * 128, generator=g, device="cuda").half()
+    v = qkv[..., (hq + hkv) * 128:].view(B, T, hkv, 128).transpose(1, 2)          # strided view, nothing contiguous
+    assert not v.is_contiguous()
+    k = comp.KEY if kind == "key" else comp.VALUE
+    a, b = comp.SparseStore(B * hkv, 512, k, "cuda"), comp.SparseStore(B * hkv, 512, k, "cuda")
+    rank = comp.keep_rank(0.7)
+    a.append(v[:, :, :256], rank)
+    a.append(v[:, :, 256:], rank)
+    b.append(v.reshape(B * hkv, T, 128).contiguous(), rank)
+    a.check(); b.check()
+    assert torch.equal(a.bitmaps[:, :a.tiles], b.bitmaps[:, :b.tiles]) and torch.equal(a.accum[:, :a.tiles + 1], b.accum[:, :b.tiles + 1])
+    for h, n in enumerate(a.packed_lengths().tolist()):
+        assert torch.equal(a.nz[h, :n].view(torch.int16), b.nz[h, :n].view(torch.int16))

@@ -17,14 +17,15 @@ def _run(lib, x, kind, rank, entry):
     nz = torch.zeros((Bh, L * 128), dtype=torch.float16, device="cuda")
     stats = torch.zeros(2, dtype=torch.int32, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
-    common = (x.data_ptr(), x.stride(0), x.stride(1), Bh, L, kind, rank, bitmaps.data_ptr(), T, accum.data_ptr(),
-              T + 1, 0, nz.data_ptr(), None, L * 128, L * 128)
+    src = (x.data_ptr(), x.stride(0), x.stride(1))
+    dst = (Bh, L, kind, rank, bitmaps.data_ptr(), T, accum.data_ptr(), T + 1, 0, nz.data_ptr(), None, L * 128, L * 128)
     if entry == "noalloc":
-        st = lib.mfar_compress_fp16_noalloc(*common, stats.data_ptr(), stats.data_ptr() + 4, stream)
+        st = lib.mfar_compress_fp16_noalloc(*src, *dst, stats.data_ptr(), stats.data_ptr() + 4, stream)
     else:
         need = lib.mfar_compress_scratch_bytes(Bh, L)
         scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
-        st = lib.mfar_compress_fp16(*common, scratch.data_ptr(), need, stats.data_ptr(), stats.data_ptr() + 4, stream)
+        st = lib.mfar_compress_fp16(*src, 0, 0, *dst, scratch.data_ptr(), need, stats.data_ptr(), stats.data_ptr() + 4,
+                                    stream)
     torch.cuda.synchronize()
     assert st == 0, st
     return bitmaps, accum, nz.view(torch.int16), stats
