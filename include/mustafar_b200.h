@@ -97,6 +97,14 @@ int mfar_compress_fp16(const void* x, int64_t x_head_stride, int64_t x_token_str
                        void* scratch, size_t scratch_bytes,
                        uint32_t* dev_status, uint32_t* max_block_halves, void* stream);
 
+/* Gathers the packed values of all heads of an arena back to back: head h (at nz + h*nz_head_stride, length
+ * 2 * accum[h*acc_head_stride + n_tiles] halves) goes behind the heads before it in `out` (out_capacity halves; a
+ * head that would not fit is skipped).  Replaces the per-head `.item()` + `clone()` loop and the model's
+ * `torch.cat` of the per-head buffers (kernel/compression.py:334-338, models/llama_mustafar_kernel.py:395).
+ * nz, out 16-byte aligned. */
+int mfar_compact_heads_fp16(const void* nz, int64_t nz_head_stride, const int32_t* accum, int64_t acc_head_stride,
+                            int64_t n_tiles, int n_heads, void* out, int64_t out_capacity, void* stream);
+
 /* The same compression for callers that cannot provide a scratch buffer because they may not
  * allocate device memory while running (a server that hands out all GPU memory from its own arena at
  * start-up, a plugin inside another runtime's budget).  No counterpart in the reference.

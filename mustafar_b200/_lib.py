@@ -25,6 +25,7 @@ SIGNATURES = {
                                   _vp, _vp, _i64, _i64, _vp, _sz, _vp, _vp, _vp]),
     "mfar_compress_fp16_noalloc": (_i32, [_vp, _i64, _i64, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _i64, _i64,
                                           _vp, _vp, _i64, _i64, _vp, _vp, _vp]),
+    "mfar_compact_heads_fp16": (_i32, [_vp, _i64, _vp, _i64, _i64, _i32, _vp, _i64, _vp]),
     "mfar_prune_fp16": (_i32, [_vp, _vp, _i64, _i64, _i32, _vp]),
     "mfar_compress_quant": (_i32, [_vp, _i64, _i64, _i32, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _i64, _vp, _vp, _vp, _vp, _vp,
                                    _i64, _i64, _vp, _i64, _i64, _vp, _vp, _sz, _vp, _vp]),

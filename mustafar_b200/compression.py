@@ -146,12 +146,16 @@ def _convert(inputs: torch.Tensor, kind: int):
     if L:
         store.append(x, 0)
     T = 2 * L
-    lengths = store.packed_lengths().tolist()      # the one host sync (the reference has 2*Bh + 1)
-    store.check()
+    host = torch.cat([store.packed_lengths(), store.stats[:1]]).tolist()   # the one host sync (the reference has 2*Bh + 1)
+    _lib.check_dev_status(host[-1], "SparseStore")
+    lengths = host[:-1]
     bitmaps = store.bitmaps[:, :T].contiguous() if store.tiles_cap != T else store.bitmaps
     accum = store.accum[:, :T + 1].contiguous() if store.tiles_cap != T else store.accum
-    # one compaction copy, then per-head views (the reference clones every head, :334-338)
-    flat = torch.cat([store.nz[h, :lengths[h]] for h in range(Bh)]) if Bh else store.nz.view(-1)[:0]
+    # one gather launch puts the heads back to back, then per-head views (the reference clones every head, :334-338)
+    flat = torch.empty(sum(lengths), dtype=torch.float16, device=x.device)
+    _lib.check(_lib.lib().mfar_compact_heads_fp16(store.nz.data_ptr(), store.nz_capacity, store.accum.data_ptr(),
+                                                  store.tiles_cap + 1, T, Bh, flat.data_ptr(), flat.numel(), _stream()),
+               "mfar_compact_heads_fp16")
     packed = list(flat.split(lengths)) if Bh else []
     return bitmaps, accum, packed
 

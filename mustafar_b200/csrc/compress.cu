@@ -237,9 +237,51 @@ __global__ void __launch_bounds__(128) prune_kernel(const __half* x, __half* y, 
     for (int j = 0; j < 8; ++j) dst[2 * j + hh] = v[j];
 }
 
+// Packed values of all heads back to back (the reference's torch.cat of per-head buffers): head h, whose values
+// lie at nz + h * nz_hs, goes to out + sum of the lengths of the heads before it.  Lengths come from the accum tails
+// on the device; grid (chunks, heads), every CTA sums the lengths in front of its head itself.
+__global__ void __launch_bounds__(256) compact_heads_kernel(const __half* nz, int64_t nz_hs, const int* acc, int64_t acc_hs,
+                                                            int64_t tiles, __half* out, int64_t out_cap) {
+    __shared__ long long s_part[8];
+    const int h = blockIdx.y;
+    long long before = 0;
+    for (int j = threadIdx.x; j < h; j += 256) before += 2ll * acc[j * acc_hs + tiles];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) before += __shfl_xor_sync(kFull, before, d);
+    if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = before;
+    __syncthreads();
+    before = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) before += s_part[w];
+    const long long len = 2ll * acc[h * acc_hs + tiles];
+    if (before + len > out_cap) return;        // never write past the caller's buffer
+    const uint4* src = reinterpret_cast<const uint4*>(nz + h * nz_hs);
+    uint4* dst = reinterpret_cast<uint4*>(out + before);
+    const long long n16 = len >> 3;
+    for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < n16; i += static_cast<long long>(gridDim.x) * 256)
+        dst[i] = src[i];
+}
+
 }  // namespace mfar
 
 using namespace mfar;
+
+extern "C" int mfar_compact_heads_fp16(const void* nz, int64_t nz_head_stride, const int32_t* accum,
+                                       int64_t acc_head_stride, int64_t n_tiles, int n_heads, void* out,
+                                       int64_t out_capacity, void* stream) {
+    if (n_heads < 0 || n_tiles < 0 || out_capacity < 0) return MFAR_ERR_ARG;
+    if (n_heads == 0 || out_capacity == 0) return MFAR_OK;
+    if (!nz || !accum || !out) return MFAR_ERR_ARG;
+    if ((reinterpret_cast<uintptr_t>(nz) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || (nz_head_stride & 7))
+        return MFAR_ERR_ALIGN;
+    if (n_heads > 65535) return MFAR_ERR_LIMIT;
+    int chunks = (device_sm_count() * 8 + n_heads - 1) / n_heads;
+    if (chunks < 1) chunks = 1;
+    compact_heads_kernel<<<dim3(chunks, n_heads), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __half*>(nz), nz_head_stride, accum, acc_head_stride, n_tiles, static_cast<__half*>(out),
+        out_capacity);
+    return launch_status();
+}
 
 extern "C" size_t mfar_compress_scratch_bytes(int n_heads, int n_tokens) {
     if (n_heads <= 0 || n_tokens <= 0) return 16;
