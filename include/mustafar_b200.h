@@ -318,6 +318,34 @@ int mfar_rope_append_f16(const void* qkv, const float* inv_freq, const int32_t* 
 /* out[r, j] = fp16(silu(gate_up[r, j])) * gate_up[r, width + j], gate_up [rows, 2*width] (HF LlamaMLP). */
 int mfar_silu_mul_f16(const void* gate_up, void* out, int64_t rows, int width, void* stream);
 
+/* One-shot all-reduce over peer-mapped buffers fused with the residual add and the RMSNorm behind it, for the
+ * tensor-parallel decode step (no counterpart in the reference, which has no distributed code; replaces an NCCL
+ * all-reduce + mfar_add_rmsnorm_f16):  x[r] += sum over ranks of partial_rank[r];  out[r] = rmsnorm(x[r]) * weight.
+ * Every rank calls it with the same arguments but its own `rank`.
+ * partials[world]  HOST array of device pointers: each rank's partial [rows, hidden] fp16 for THIS call, as mapped
+ *                  into this process (CUDA IPC or any peer mapping; partials[rank] is local).  Callers alternate
+ *                  between two buffers from call to call.
+ * flags[world]     HOST array of device pointers: each rank's flag array (8 uint32, zero at start-up).
+ * epoch of a call = step * calls_per_step + call + 1, step read from step_dev (device int32) when not NULL; it must
+ *                  grow from call to call, the same on every rank.
+ * wait_ns          bound on the wait for the peers' flags; when it runs out MFAR_DEV_TIMEOUT is set in *dev_status and
+ *                  x / out are left untouched.  Plain loads and stores over NVLink only: no TMA, no multicast. */
+int mfar_peer_reduce_add_rmsnorm_f16(void* x, const void* const* partials, void* const* flags, int world, int rank,
+                                     const int32_t* step_dev, int step, int calls_per_step, int call,
+                                     const void* weight, void* out, int64_t rows, int hidden, float eps,
+                                     int64_t wait_ns, uint32_t* dev_status, void* stream);
+
+/* Set-up of the buffers mfar_peer_reduce_add_rmsnorm_f16 reads across GPUs (one-off, not on the hot path).
+ * mfar_peer_alloc: cudaMalloc of `bytes` zeroed bytes on the current device, *ptr = the allocation, handle64 (64 host
+ *                  bytes) = its CUDA IPC handle, to be sent to the other ranks' processes by any host channel.
+ * mfar_peer_open:  maps a peer's handle with THIS process's GPU current, so that its kernels can read and write the
+ *                  memory over NVLink (a mapping opened with the owner's device current is only good for copies).
+ * mfar_peer_close / mfar_peer_free undo the two; close every mapping before its owner frees the allocation. */
+int mfar_peer_alloc(int64_t bytes, void** ptr, void* handle64);
+int mfar_peer_open(const void* handle64, void** ptr);
+int mfar_peer_close(void* ptr);
+int mfar_peer_free(void* ptr);
+
 #ifdef __cplusplus
 }
 #endif

@@ -4,7 +4,8 @@
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 -m mustafar_b200.e2e_llama --parallel tp
 
 Random-init fp16 weights (seeded), uniformly random prompt ids, greedy decoding.  `tp` = 8-way
-(or world-size-way) head tensor parallelism with an NCCL all-reduce after o_proj and down_proj;
+(or world-size-way) head tensor parallelism: the partial sums after o_proj and down_proj meet in a peer-buffer
+reduction fused with the residual add + RMSNorm (`--tp-reduce fused`, the default) or in NCCL all-reduces (`nccl`);
 `dp` = every rank runs the whole model on its own `--batch` sequences (no collective).
 Prints one JSON line on rank 0: prefill time, time per output token and decode tokens/s of the
 whole job, measured with CUDA events, maximum over ranks.
@@ -23,14 +24,38 @@ from .sharding import max_over_ranks
 
 def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 4096, new: int = 256,
             parallel: str = "dp", sparsity: float = 0.7, layers: int = 32, graph: bool = True, dense: bool = False,
-            bits: int = 16, prune_mode: str = "block") -> dict:
+            bits: int = 16, prune_mode: str = "block", tp_reduce: str = "fused") -> dict:
     """One generation (prefill + ``new`` greedy steps) on this rank's GPU; returns the result record (the same on
-    every rank: times are the maximum over ranks).  ``dist``: an initialised torch.distributed module or None."""
+    every rank: times are the maximum over ranks).  ``dist``: an initialised torch.distributed module or None.
+    ``tp_reduce``: "fused" = peer-buffer reduction fused with the RMSNorm, whole step one CUDA graph; "nccl" = NCCL
+    all-reduces between graphs (also what "fused" falls back to when the peer mapping cannot be set up)."""
     tp = world if parallel == "tp" else 1
     shape = LlamaShape(n_layers=layers)
-    model = SparseLlama(shape, batch, prompt + new, dev, sparsity=sparsity, seed=1234,
-                        tp_rank=rank if tp > 1 else 0, tp_world=tp, dist=dist, sparse=not dense, cache_bits=bits,
-                        prune_mode=prune_mode)
+    kw = dict(sparsity=sparsity, seed=1234, tp_rank=rank if tp > 1 else 0, tp_world=tp, dist=dist, sparse=not dense,
+              cache_bits=bits, prune_mode=prune_mode)
+    reduce_used = "none"
+    if tp > 1:
+        reduce_used = "nccl"
+        ok = torch.zeros(1, device=dev)
+        model = None
+        if tp_reduce == "fused" and not dense:
+            try:
+                model = SparseLlama(shape, batch, prompt + new, dev, tp_fused=True, **kw)
+                ok += 1
+            except Exception as e:      # e.g. CUDA IPC not permitted between the ranks' containers
+                if rank == 0:
+                    print(f"peer-buffer reduction unavailable ({type(e).__name__}: {e}); using NCCL", flush=True)
+                model = None
+            dist.all_reduce(ok)          # all ranks or none
+            if int(ok.item()) == world:
+                reduce_used = "fused peer buffers"
+            else:
+                model = None
+        if model is None:
+            torch.cuda.empty_cache()
+            model = SparseLlama(shape, batch, prompt + new, dev, **kw)
+    else:
+        model = SparseLlama(shape, batch, prompt + new, dev, **kw)
     g = torch.Generator(device=dev).manual_seed(99 if tp > 1 else 99 + rank)
     toks = torch.randint(0, shape.vocab, (batch, prompt), generator=g, device=dev)
 
@@ -72,6 +97,8 @@ def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 409
             else:
                 per += (8 + 4 + 2 + 2) * tiles + 4.0 * float(st.head_tail.float().mean())
         cache_bytes = per / model.compressed
+    if getattr(model, "peer", None) is not None:
+        model.peer.close()
     del model
     torch.cuda.empty_cache()
     return {
@@ -82,10 +109,10 @@ def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 409
         "config": {"workload": f"Llama-3-8B shape, {layers} layers, prompt {prompt}, {new} new tokens, "
                                f"batch {batch} per {'job' if tp > 1 else 'GPU'}, sparsity {sparsity}, window 128, "
                                f"pruning per {prune_mode}",
-                   "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}",
+                   "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}", "partial_sum_reduction": reduce_used,
                    "cache": "dense-pruned torch" if dense else ("sparse fp16" if bits == 16 else f"sparse {bits}-bit"),
                    "cuda_graph": (False if (not graph or dense) else
-                                  ("one graph per stretch between collectives" if tp > 1 else True))},
+                                  ("one graph per stretch between collectives" if reduce_used == "nccl" else True))},
         "data": "synthetic (random-init weights, random prompt ids)", "dtype": "f16"}
 
 
@@ -101,6 +128,8 @@ def main():
     ap.add_argument("--dense", action="store_true", help="dense pruned cache + torch attention (comparison arm)")
     ap.add_argument("--bits", type=int, default=16, choices=[16, 4, 2],
                     help="16: pruned values kept as fp16; 4 / 2: quantised per tile")
+    ap.add_argument("--tp-reduce", default="fused", choices=["fused", "nccl"],
+                    help="tensor parallel only: partial sums through the fused peer-buffer kernel or through NCCL")
     ap.add_argument("--prune-mode", default="block", choices=["block", "step"],
                     help="block: prune with the compression, 256 tokens at a time; step: prune the token that leaves "
                          "the residual window at every decode step")
@@ -114,7 +143,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     res = run_e2e(dev, rank, world, dist, a.batch, a.prompt, a.new, a.parallel, a.sparsity, a.layers, not a.no_graph,
-                  a.dense, a.bits, a.prune_mode)
+                  a.dense, a.bits, a.prune_mode, a.tp_reduce)
     if rank == 0:
         print(json.dumps(res))
     if dist is not None:

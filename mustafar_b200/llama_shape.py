@@ -76,7 +76,7 @@ class SparseLlama:
 
     def __init__(self, shape: LlamaShape, batch: int, max_tokens: int, device, sparsity: float = 0.7,
                  residual: int = 128, seed: int = 0, tp_rank: int = 0, tp_world: int = 1, dist=None,
-                 sparse: bool = True, cache_bits: int = 16, prune_mode: str = "block"):
+                 sparse: bool = True, cache_bits: int = 16, prune_mode: str = "block", tp_fused: bool = False):
         assert shape.n_kv_heads % tp_world == 0 and shape.ffn % tp_world == 0
         self.s, self.B, self.dev = shape, batch, torch.device(device)
         self.sparsity, self.residual, self.sparse = sparsity, residual, sparse
@@ -147,6 +147,12 @@ class SparseLlama:
         # the decode calls of this model write their split records here: a buffer of its own, sized for the full
         # cache, so that captured graphs never see it move and other users of the ops cannot grow it away
         self.prefill_compress_ms = self.prefill_attention_ms = 0.0
+        # tensor parallel decode: partial sums meet in NCCL all-reduces between CUDA graphs, or (tp_fused) in the
+        # peer-buffer reduction fused with the residual add + RMSNorm, which lets the whole step be one graph
+        self.peer = None
+        if tp_world > 1 and tp_fused and sparse:
+            from .peer import PeerGroup
+            self.peer = PeerGroup(dist, tp_rank, tp_world, self.dev, batch, shape.hidden, 2 * shape.n_layers)
         self._decode_ws = None
         if self.sparse:
             _, nbytes = ops.plan(batch * self.hkv, self.max_tokens, self.wcap, self.G)
@@ -291,11 +297,30 @@ class SparseLlama:
         hint = 0 if (dev_state or self.quant) else self._hint()
         w = self.wlen
         pr = dict(prune_rank=self.rank_keep, prune_back=self.residual) if self.step_prune else {}
-        tp = self.tp_world > 1
+        peer = self.peer
+        tp = self.tp_world > 1 and peer is None
         x = self.embed[token]                     # [B, hidden], updated in place from here on
         delta = None
+        call = 0                                  # peer reductions issued so far in this step
+
+        def add_norm(delta, w):
+            """residual add + RMSNorm; with peer buffers `delta` is the partial left in slot(call - 1) by the GEMM"""
+            if peer is not None and delta is not None:
+                return peer.reduce_add_rmsnorm(x, call - 1, w, eps)
+            return step_ops.add_rmsnorm(x, delta, w, eps)
+
+        def row_parallel(inp, w):
+            """GEMM whose output is a partial sum over ranks: straight into the peer-visible buffer when there is one"""
+            nonlocal call
+            if peer is None:
+                return F.linear(inp, w)
+            out = peer.slot(call)
+            torch.mm(inp, w.t(), out=out)
+            call += 1
+            return out
+
         for L in self.layers:
-            h = step_ops.add_rmsnorm(x, delta, L.n1, eps)
+            h = add_norm(delta, L.n1)
             qkv = F.linear(h, L.wqkv)
             if dev_state and self.quant:
                 step_ops.rope_append(qkv, self._inv_freq, self._state[0:1], self._state[1:2], self.hq, self.hkv,
@@ -319,16 +344,18 @@ class SparseLlama:
                 step_ops.rope_append(qkv, self._inv_freq, self.tokens, w, self.hq, self.hkv, self._qbuf, L.kwin, L.vwin, **pr)
                 att = ops.decode_attention(self._qbuf, L.ks, L.vs, L.kwin[:, :w + 1], L.vwin[:, :w + 1], self.G,
                                            stage_halves=hint, workspace=self._decode_ws)
-            o = F.linear(att.view(B, self.hq * D), L.wo)
+            o = row_parallel(att.view(B, self.hq * D), L.wo)
             if tp:
                 yield o
-            h = step_ops.add_rmsnorm(x, o, L.n2, eps)
-            delta = F.linear(step_ops.silu_mul(F.linear(h, L.wgu)), L.wd)
+            h = add_norm(o, L.n2)
+            delta = row_parallel(step_ops.silu_mul(F.linear(h, L.wgu)), L.wd)
             if tp:
                 yield delta
         if dev_state:
             self._state += self._state_step
-        self._step_out = F.linear(step_ops.add_rmsnorm(x, delta, self.norm, eps), self.lm_head)
+        self._step_out = F.linear(add_norm(delta, self.norm), self.lm_head)
+        if peer is not None:
+            peer.end_step()
 
     def _step_body_fused(self, token: torch.Tensor, dev_state: bool) -> torch.Tensor:
         for partial in self._step_segments(token, dev_state):

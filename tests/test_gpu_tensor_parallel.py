@@ -1,5 +1,6 @@
-"""Head tensor parallelism of the model glue over NCCL (all-reduce after o_proj / down_proj): needs
-two GPUs; skipped on a single-GPU box.  The ranks are child processes started by torch.distributed.run."""
+"""Head tensor parallelism of the model glue (partial sums after o_proj / down_proj meet in NCCL all-reduces, or in
+the peer-buffer reduction fused with the RMSNorm): needs two GPUs; skipped on a single-GPU box.  The ranks are child
+processes started by torch.distributed.run; NVLS is switched off for NCCL and the fused kernel uses plain peer loads."""
 import os
 import subprocess
 import sys
@@ -12,9 +13,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("fused", ["0", "1"])
 @pytest.mark.parametrize("graph", ["0", "1"])
-def test_tp2_matches_single_gpu(graph):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_WORKER_GRAPH=graph)
+def test_tp2_matches_single_gpu(graph, fused):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_WORKER_GRAPH=graph, TP_WORKER_FUSED=fused)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
            "127.0.0.1", "--master-port", "29661", os.path.join(HERE, "tp_worker.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)

@@ -16,7 +16,9 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     shape, B, prompt = tiny_shape(), 2, 256 + 128 + 100
     toks = torch.randint(0, shape.vocab, (B, prompt), device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
-    tp = SparseLlama(shape, B, 1024, "cuda", seed=11, tp_rank=rank, tp_world=world, dist=dist)
+    fused = os.environ.get("TP_WORKER_FUSED", "0") == "1"   # peer-buffer reduction fused with the RMSNorm instead of NCCL
+    tp = SparseLlama(shape, B, 1024, "cuda", seed=11, tp_rank=rank, tp_world=world, dist=dist, tp_fused=fused)
+    assert (tp.peer is not None) == fused
     lt = tp.prefill(toks)
     ref = SparseLlama(shape, B, 1024, "cuda", seed=11) if rank == 0 else None
     lr = ref.prefill(toks) if rank == 0 else None
@@ -31,9 +33,13 @@ def main():
             lr = ref.decode_step(nxt)
             err = float(torch.linalg.norm(lt.float() - lr.float()) / torch.linalg.norm(lr.float()))
             worst = max(worst, err)
+    from mustafar_b200 import ops
+    ops.check_device_status()
     if rank == 0:
         print("TP_WORST_REL_L2", worst, flush=True)
         assert worst < 5e-3, worst
+    if tp.peer is not None:
+        tp.peer.close()
     dist.barrier()
     dist.destroy_process_group()
 
