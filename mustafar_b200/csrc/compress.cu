@@ -19,9 +19,8 @@
 
 namespace mfar {
 
-#ifndef MFAR_COMPRESS_MIN_CTAS
-#define MFAR_COMPRESS_MIN_CTAS 5
-#endif
+// resident CTAs per SM the register allocation aims at: 96 registers, no spills (6 would spill the bit planes)
+constexpr int kCompressMinCtas = 5;
 
 struct CompressParams {
     const __half* x;
@@ -44,7 +43,7 @@ struct CompressParams {
 };
 
 template <int KIND>
-__global__ void __launch_bounds__(128, MFAR_COMPRESS_MIN_CTAS) compress_kernel(CompressParams p) {
+__global__ void __launch_bounds__(128, kCompressMinCtas) compress_kernel(CompressParams p) {
     __shared__ __align__(16) unsigned short ps[64 * 128];                                       // packed values, final order
     __shared__ __align__(16) unsigned short xs[KIND == MFAR_KIND_KEY ? 64 * kXsStride : 8];     // K: the raw block
     __shared__ unsigned s_mask[4][64];         // K: keep flags [32-channel word][row], first channel in the top bit

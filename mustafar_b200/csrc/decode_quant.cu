@@ -15,12 +15,6 @@
 //     fp16), with the scale folded into the per-tile coefficients; fp32 accumulation.
 #include "decode_common.cuh"
 
-#ifndef MFAR_Q_STEP_UNROLL
-#define MFAR_Q_STEP_UNROLL 8
-#endif
-#define MFAR_Q_PRAGMA(x) _Pragma(#x)
-#define MFAR_Q_UNROLL_N(n) MFAR_Q_PRAGMA(unroll n)
-#define MFAR_Q_UNROLL MFAR_Q_UNROLL_N(MFAR_Q_STEP_UNROLL)
 
 namespace mfar {
 
@@ -212,7 +206,7 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
             for (int t = 0; t < 8; ++t)
 #pragma unroll
                 for (int g = 0; g < G; ++g) acc_s[t][g] = 0.f;
-MFAR_Q_UNROLL
+#pragma unroll 8
             for (int s = 0; s < 32 / 4; ++s) {
                 const int c = warp * 32 + s * 4 + gi;
                 const uint2 bm = kbf.bm[c];
@@ -290,7 +284,7 @@ MFAR_Q_UNROLL
             }
         }
         const int half_id = gi & 1, par = gi >> 1;
-MFAR_Q_UNROLL
+#pragma unroll 8
         for (int s = 0; s < 16 / 2; ++s) {
             const int t = warp * 16 + s * 2 + par;
             const int tile = half_id * 64 + t;

@@ -8,7 +8,9 @@
 //   1. announces "my partial of call `epoch` is complete" by storing the epoch into slot [rank] of every peer's flag
 //      array (plain system-scope stores over NVLink; the partial was written by the previous kernel on this stream);
 //   2. waits until its own flag array shows the epoch for every peer.  The wait is bounded by `wait_ns`: when it runs
-//      out the CTA records MFAR_DEV_TIMEOUT and leaves without touching x or out (no trap, the context stays usable);
+//      out the CTA records MFAR_DEV_TIMEOUT and leaves without touching x or out (no trap, the context stays usable).
+//      The bit is sticky: launches that find it set still announce, but do not wait again, so a step of 64 reductions
+//      replayed from a CUDA graph costs one bound, not 64, before the host sees the error;
 //   3. reads the peers' rows with plain L1-bypassing loads through the peer pointers (no TMA, no multicast of any
 //      kind), sums them in rank order in fp32 - the same order on every rank, so all ranks get identical bits -
 //      adds the residual and normalises.
@@ -69,10 +71,12 @@ __global__ void __launch_bounds__(256) peer_reduce_rmsnorm_kernel(PeerReducePara
     if (tid < p.world) {
         const unsigned* f = p.flags[p.rank] + tid;
         const unsigned long long t0 = global_timer_ns();
-        bool ok = true;
+        // an earlier reduction already gave up: the group is broken, look once and do not wait
+        const bool broken = p.dev_status && (ld_volatile_u32(p.dev_status) & MFAR_DEV_TIMEOUT);
+        bool ok = !(broken && static_cast<int>(ld_sys_u32(f) - epoch) < 0);
         unsigned spins = 0;
-        while (static_cast<int>(ld_sys_u32(f) - epoch) < 0) {
-            if ((++spins & 63u) == 0 && global_timer_ns() - t0 > p.wait_ns) { ok = false; break; }
+        while (ok && static_cast<int>(ld_sys_u32(f) - epoch) < 0) {
+            if ((++spins & 63u) == 0 && global_timer_ns() - t0 > p.wait_ns) ok = false;
         }
         if (!ok) s_ok = 0;
     }

@@ -138,7 +138,7 @@ def bench_compress_fp16(quick):
 
         def runq():
             _lib.check(_lib.lib().mfar_compress_quant(
-                x.data_ptr(), x.stride(0), x.stride(1), Bh, L, kind, comp.keep_rank(0.7), 2, 64,
+                x.data_ptr(), x.stride(0), x.stride(1), 0, 0, Bh, L, kind, comp.keep_rank(0.7), 2, 64,
                 bufs[0].data_ptr(), T, bufs[1].data_ptr(), bufs[2].data_ptr(), bufs[3].data_ptr(), bufs[4].data_ptr(),
                 bufs[5].data_ptr(), T, 0, packed.data_ptr(), 0, worst, info.data_ptr(), scratch.data_ptr(), need,
                 info.data_ptr() + 4 * Bh, torch.cuda.current_stream().cuda_stream), "mfar_compress_quant")
@@ -226,11 +226,12 @@ def bench_ops(quick):
     ops.check_device_status()
 
 
-def bench_quant(quick):
+def bench_quant(quick, batch=None, kv_len=None, bit_list=(2, 4), sparsities=(0.5, 0.7)):
     B, L = (2, 4096) if quick else (32, 16384)
+    B, L = batch or B, kv_len or L
     Bh = B * HKV
-    for s in (0.5, 0.7):
-        for bits in (2, 4):
+    for s in sparsities:
+        for bits in bit_list:
             kq = cq.compress_quant(synth(Bh, L, 21, True), comp.KEY, comp.keep_rank(s), bits, 64)
             vq = cq.compress_quant(synth(Bh, L, 22, False), comp.VALUE, comp.keep_rank(s), bits, 64)
             kw, vw = synth(Bh, 128, 1, True), synth(Bh, 128, 2, False)
@@ -243,14 +244,49 @@ def bench_quant(quick):
     ops.check_device_status()
 
 
+def bench_step(quick):
+    """The launches around the attention call in one decode step of one layer (Llama-3-8B shape): RoPE + window append
+    with and without the per-step pruning of the token that leaves the 128 most recent ones, residual add + RMSNorm,
+    SiLU * up.  Replayed CUDA graphs (these kernels take a few microseconds)."""
+    from . import step_ops
+    B, cap, hidden, ffn = (4 if quick else 32), 384, 4096, 14336
+    qkv = torch.randn(B, (HQ + 2 * HKV) * D, device="cuda").half()
+    inv = step_ops.rope_inv_freq(500000.0, "cuda")
+    q_out = torch.empty(B * HQ, D, dtype=torch.float16, device="cuda")
+    kwin, vwin = synth(B * HKV, cap, 32, True), synth(B * HKV, cap, 33, False)
+    io = 2 * qkv.numel() * 2
+    for name, kw, extra in (("RoPE + window append", {}, 0),
+                            ("RoPE + window append + prune of the token leaving the window (1 token/step)",
+                             dict(prune_rank=comp.keep_rank(0.7), prune_back=128), 2 * 2 * B * HKV * D * 2)):
+        us = timed_graph(lambda: step_ops.rope_append(qkv, inv, 5000, 300, HQ, HKV, q_out, kwin, vwin, **kw))
+        emit(name, us, io + extra, batch=B, q_heads=HQ, kv_heads=HKV)
+    x = torch.randn(B, hidden, device="cuda").half()
+    d = torch.randn(B, hidden, device="cuda").half()
+    w = torch.ones(hidden, device="cuda").half()
+    o = torch.empty_like(x)
+    us = timed_graph(lambda: step_ops.add_rmsnorm(x, d, w, 1e-5, out=o))
+    emit("residual add + RMSNorm", us, 4 * x.numel() * 2 + hidden * 2, batch=B, hidden=hidden)
+    gu = torch.randn(B, 2 * ffn, device="cuda").half()
+    so = torch.empty(B, ffn, dtype=torch.float16, device="cuda")
+    us = timed_graph(lambda: step_ops.silu_mul(gu, out=so))
+    emit("SiLU(gate) * up", us, 3 * B * ffn * 2, batch=B, width=ffn)
+    ops.check_device_status()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="compress,decode,ops,quant")
+    ap.add_argument("--what", default="compress,decode,decode_groups,ops,quant,step")
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--quant-case", default="", help="batch,kv_len,bits,sparsity: run the quantised decode on this one case "
+                                                     "(a small one to put under a profiler)")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("needs a CUDA device")
-    table = {"compress": bench_compress, "compress_fp16": bench_compress_fp16, "decode_groups": bench_decode_groups, "decode": bench_decode, "ops": bench_ops, "quant": bench_quant}
+    table = {"compress": bench_compress, "compress_fp16": bench_compress_fp16, "decode_groups": bench_decode_groups, "decode": bench_decode, "ops": bench_ops, "quant": bench_quant, "step": bench_step}
+    if a.quant_case:
+        b, l, bits, sp = a.quant_case.split(",")
+        bench_quant(False, int(b), int(l), (int(bits),), (float(sp),))
+        return
     for w in a.what.split(","):
         table[w](a.quick)
 

@@ -61,6 +61,12 @@ def test_missing_peer_signal_times_out_and_writes_nothing():
     torch.cuda.synchronize()
     assert int(status) & _lib.DEV_TIMEOUT
     assert torch.equal(x, x0) and float(out.abs().sum()) == 0.0
+    # the bit is sticky: the next unsignalled call gives up at once instead of waiting for its own bound (10 s here)
+    import time
+    t0 = time.perf_counter()
+    assert call(lib, x, parts, flags, step, 1, w, out, status, 10000) == 0
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0 and torch.equal(x, x0)
     # the context is still usable and a later, signalled call succeeds
     flags[0][1] = 100
     status.zero_()
