@@ -337,9 +337,14 @@ def main():
         from mustafar_b200.e2e_llama import run_e2e
         del ks, vs, kw, vw, ws
         torch.cuda.empty_cache()
-        e2e_llama = {"batch_sharded": run_e2e(dev, rank, world, dist, new=a.e2e_llama_new, parallel="dp")}
-        if world == 8:
-            e2e_llama["tensor_parallel"] = run_e2e(dev, rank, world, dist, new=a.e2e_llama_new, parallel="tp")
+        e2e_llama = {}
+        arms = [("batch_sharded", "dp")] + ([("tensor_parallel", "tp")] if world == 8 else [])
+        for name, par in arms:
+            try:        # the headline line is printed whatever happens here
+                e2e_llama[name] = run_e2e(dev, rank, world, dist, new=a.e2e_llama_new, parallel=par)
+            except Exception as e:
+                e2e_llama[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+                torch.cuda.empty_cache()
 
     if rank == 0:
         peak, which = measured_peak_gbs()

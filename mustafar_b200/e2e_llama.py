@@ -22,6 +22,26 @@ from .llama_shape import LlamaShape, SparseLlama
 from .sharding import max_over_ranks
 
 
+def _check_peer_reduction(peer, dist, dev) -> None:
+    """One fused reduction on known data against NCCL's sum of the same partials, before the buffers are trusted with
+    the timed run; raises when the two disagree or a wait ran out.  Leaves the group's step counter one step on."""
+    from . import ops
+    g = torch.Generator(device=dev).manual_seed(4242 + peer.rank)
+    part = (torch.randn(peer.rows, peer.hidden, generator=g, device=dev) * 0.1).half()
+    x = torch.ones(peer.rows, peer.hidden, dtype=torch.float16, device=dev)
+    w = torch.ones(peer.hidden, dtype=torch.float16, device=dev)
+    peer.slot(0).copy_(part)
+    peer.reduce_add_rmsnorm(x, 0, w, 1e-5)
+    peer.end_step()
+    total = part.float()
+    dist.all_reduce(total)
+    torch.cuda.synchronize()
+    ops.check_device_status(dev)
+    err = float((x.float() - (1.0 + total)).abs().max())
+    if not err < 2e-2:      # fp16 rounding of 1 + sum of `world` partials of size ~0.1
+        raise RuntimeError(f"peer reduction disagrees with NCCL (max abs error {err})")
+
+
 def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 4096, new: int = 256,
             parallel: str = "dp", sparsity: float = 0.7, layers: int = 32, graph: bool = True, dense: bool = False,
             bits: int = 16, prune_mode: str = "block", tp_reduce: str = "fused") -> dict:
@@ -41,6 +61,7 @@ def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 409
         if tp_reduce == "fused" and not dense:
             try:
                 model = SparseLlama(shape, batch, prompt + new, dev, tp_fused=True, **kw)
+                _check_peer_reduction(model.peer, dist, dev)
                 ok += 1
             except Exception as e:      # e.g. CUDA IPC not permitted between the ranks' containers
                 if rank == 0:
@@ -77,8 +98,18 @@ def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 409
         marks[-1].record()
     e[2].record()
     torch.cuda.synchronize()
+    # device-reported errors (a wait that ran out, corrupt metadata): every rank learns of them, so that all raise together
+    from . import ops
+    flagged = ops._dev_status(dev).to(torch.float32).clone()
+    if dist is not None:
+        dist.all_reduce(flagged, op=dist.ReduceOp.MAX)
+    if float(flagged) != 0.0:
+        ops.check_device_status(dev)
+        raise RuntimeError("another rank reported a device error during the generation")
     # per-step device time: the median leaves out the steps that append a block or capture the graph
-    gaps = sorted(x.elapsed_time(y) for x, y in zip(marks[:-1], marks[1:]))
+    raw_gaps = [x.elapsed_time(y) for x, y in zip(marks[:-1], marks[1:])]
+    slowest_at = (max(range(len(raw_gaps)), key=raw_gaps.__getitem__) + 1) if raw_gaps else -1   # 0-based decode step
+    gaps = sorted(raw_gaps)
     steady_ms = max_over_ranks(gaps[len(gaps) // 2], dist, dev) if gaps else 0.0
     slowest_ms = max_over_ranks(gaps[-1], dist, dev) if gaps else 0.0
     prefill_ms = max_over_ranks(e[0].elapsed_time(e[1]), dist, dev)
@@ -104,7 +135,7 @@ def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 409
     return {
         "metric": "llama3_8b_shape_decode_throughput", "unit": "tok/s", "n_gpus": world,
         "value": seqs * (new - 1) / (decode_ms * 1e-3), "tpot_ms": decode_ms / (new - 1), "tpot_median_ms": steady_ms,
-        "slowest_step_ms": slowest_ms, "ttft_ms": prefill_ms, "ttft_compression_ms": compress_ms,
+        "slowest_step_ms": slowest_ms, "slowest_step_index": slowest_at, "ttft_ms": prefill_ms, "ttft_compression_ms": compress_ms,
         "compressed_cache_bytes_per_token_per_kv_head": cache_bytes, "dense_fp16_bytes_per_token_per_kv_head": 512,
         "config": {"workload": f"Llama-3-8B shape, {layers} layers, prompt {prompt}, {new} new tokens, "
                                f"batch {batch} per {'job' if tp > 1 else 'GPU'}, sparsity {sparsity}, window 128, "

@@ -24,6 +24,18 @@ MAX_PEERS = 8
 _FLAG_BYTES = 256          # 8 uint32 flags, padded so that the partials start 256-byte aligned
 
 
+def epoch_of(step: int, calls_per_step: int, call: int) -> int:
+    """Epoch the kernel derives for reduction ``call`` of step ``step`` (what it writes into the peers' flags)."""
+    return step * calls_per_step + call + 1
+
+
+def slot_of(call: int) -> int:
+    """Partial buffer (0 or 1) reduction ``call`` of a step uses.  The choice is made on the host, at graph-capture
+    time, so it cannot depend on the step: consecutive reductions alternate across step boundaries only when the number
+    of calls per step is even, which PeerGroup therefore requires."""
+    return call & 1
+
+
 class _DeviceView:
     """Lets torch view a raw device allocation (torch.as_tensor reads ``__cuda_array_interface__``)."""
 
@@ -36,6 +48,9 @@ class PeerGroup:
                  wait_ms: float = 2000.0):
         if world > MAX_PEERS:
             raise RuntimeError(f"at most {MAX_PEERS} ranks")
+        if calls_per_step <= 0 or calls_per_step % 2:
+            raise RuntimeError("calls_per_step must be even: the two partial buffers alternate from call to call, also "
+                               "from the last call of a step to the first of the next")
         self.rank, self.world, self.dev = rank, world, torch.device(device)
         self.rows, self.hidden, self.calls_per_step = rows, hidden, calls_per_step
         self.wait_ns = int(wait_ms * 1e6)
@@ -86,7 +101,7 @@ class PeerGroup:
 
     def slot(self, call: int) -> torch.Tensor:
         """The local partial buffer of call ``call`` of a step: the producer (a GEMM with ``out=``) writes here."""
-        return self.partials[call & 1]
+        return self.partials[slot_of(call)]
 
     def reduce_add_rmsnorm(self, x: torch.Tensor, call: int, weight: torch.Tensor, eps: float,
                            out: torch.Tensor | None = None) -> torch.Tensor:
@@ -97,7 +112,7 @@ class PeerGroup:
         if out is None:
             out = torch.empty_like(x)
         st = _lib.lib().mfar_peer_reduce_add_rmsnorm_f16(
-            x.data_ptr(), self._ptr_arrays[call & 1], self._flag_array, self.world, self.rank, self.step.data_ptr(), 0,
+            x.data_ptr(), self._ptr_arrays[slot_of(call)], self._flag_array, self.world, self.rank, self.step.data_ptr(), 0,
             self.calls_per_step, call, weight.data_ptr(), out.data_ptr(), self.rows, self.hidden, float(eps),
             self.wait_ns, _dev_status(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
         _lib.check(st, "mfar_peer_reduce_add_rmsnorm_f16")

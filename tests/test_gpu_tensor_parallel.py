@@ -22,3 +22,13 @@ def test_tp2_matches_single_gpu(graph, fused):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
     assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
     assert "TP_WORST_REL_L2" in r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_peer_wait_runs_out_when_a_rank_stays_silent():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29663", os.path.join(HERE, "peer_timeout_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
+    assert "PEER_TIMEOUT_OK" in r.stdout
