@@ -19,8 +19,11 @@
 
 namespace mfar {
 
-// resident CTAs per SM the register allocation aims at: 96 registers, no spills (6 would spill the bit planes)
-constexpr int kCompressMinCtas = 5;
+// resident CTAs per SM the register allocation aims at.  K tiles: 5 (96 registers; at 6 the bit planes spill and the
+// kernel is 20 % slower).  V tiles: 6 (80 registers, 4 bytes of spill, 6 % faster: the V pack works from registers
+// and has no column walk that the spill could delay).
+constexpr int kCompressMinCtasKey = 5;
+constexpr int kCompressMinCtasValue = 6;
 
 struct CompressParams {
     const __half* x;
@@ -43,7 +46,7 @@ struct CompressParams {
 };
 
 template <int KIND>
-__global__ void __launch_bounds__(128, kCompressMinCtas) compress_kernel(CompressParams p) {
+__global__ void __launch_bounds__(128, KIND == MFAR_KIND_KEY ? kCompressMinCtasKey : kCompressMinCtasValue) compress_kernel(CompressParams p) {
     __shared__ __align__(16) unsigned short ps[64 * 128];                                       // packed values, final order
     __shared__ __align__(16) unsigned short xs[KIND == MFAR_KIND_KEY ? 64 * kXsStride : 8];     // K: the raw block
     __shared__ unsigned s_mask[4][64];         // K: keep flags [32-channel word][row], first channel in the top bit
