@@ -52,7 +52,29 @@ def parse():
     ap.add_argument("--no-e2e-llama", action="store_true",
                     help="skip the end-to-end Llama-3-8B-shape generation reported under \"e2e_llama\"")
     ap.add_argument("--e2e-llama-new", type=int, default=256, help="generated tokens of the end-to-end run")
+    ap.add_argument("--no-other-configs", action="store_true",
+                    help="skip the short measurements of the other workloads reported under \"other_configs\"")
     return ap.parse_args()
+
+
+def other_configs():
+    """Short timings of the remaining workloads through the same library (mustafar_b200/kernel_bench.py runs them)."""
+    from mustafar_b200 import kernel_bench as kb
+    peak, _ = measured_peak_gbs()
+    rows = []
+
+    def collect(name, us, nbytes, **kw):
+        rows.append({"kernel": name, "us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1),
+                     "frac_of_hbm_peak": round(nbytes / us / 1e3 / peak, 3), **kw})
+    emit, kb.emit = kb.emit, collect
+    try:
+        kb.bench_compress_fp16(False, iters=10, warmup=3)
+        kb.bench_quant(False, 32, 16384, (2,), (0.7,))
+        kb.bench_step(False)
+    finally:
+        kb.emit = emit
+        torch.cuda.empty_cache()
+    return rows
 
 
 # ------------------------------------------------------------------------------------------ peaks / clocks
@@ -346,6 +368,16 @@ def main():
                 e2e_llama[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
                 torch.cuda.empty_cache()
 
+    # the other workloads of the path, a few calls each, so that one bench line shows them all (N = 1 only; their
+    # parity is what the -m gpu tests check, here they are only timed): prune + compress of 64 heads x 8192 tokens,
+    # the decode over the 2-bit cache at batch 32 x 16384 tokens, the per-step launches around the attention call
+    other = None
+    if world == 1 and not a.no_other_configs:
+        try:
+            other = other_configs()
+        except Exception as e:
+            other = {"error": f"{type(e).__name__}: {e}"[:300]}
+
     if rank == 0:
         peak, which = measured_peak_gbs()
         achieved = alg_bytes / (per_launch_ms * 1e-3) / 1e9
@@ -362,6 +394,7 @@ def main():
             "gpu_launches": a.steps,
             "parity_check": parity,
             "e2e_llama": e2e_llama,
+            "other_configs": other,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": which, "frac_of_nominal_8000": achieved / 8000.0,
                          "algorithmic_bytes_per_launch": alg_bytes,

@@ -669,31 +669,4 @@ int launch_decode_attn_quant(const DecodeParams& p, int G, int bits, bool group3
     return MFAR_ERR_ARG;
 }
 
-int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G, const void* kwin, const void* vwin,
-                         int64_t win_hs, int64_t win_ts, int W, const int* W_dev, float softmax_scale, float* ws,
-                         int rec_index, unsigned* dev_status, cudaStream_t s, bool halves8) {
-    if (!kwin || !vwin || !q) return MFAR_ERR_ARG;
-    if ((reinterpret_cast<uintptr_t>(kwin) & 15) || (reinterpret_cast<uintptr_t>(vwin) & 15) || (win_hs & 7) ||
-        (win_ts & 7) || (reinterpret_cast<uintptr_t>(q) & 3) || (q_stride & 1))
-        return MFAR_ERR_ALIGN;
-    DecodeParams p{};
-    p.q = static_cast<const __half*>(q);
-    p.q_stride = q_stride;
-    p.kwin = static_cast<const __half*>(kwin);
-    p.vwin = static_cast<const __half*>(vwin);
-    p.win_hs = win_hs;
-    p.win_ts = win_ts;
-    p.W = W;
-    p.W_dev = W_dev;
-    p.nsplit = rec_index;
-    p.split_offset = rec_index;
-    p.nrec = rec_index + 1;
-    p.rec_group = (halves8 && G == 8) ? 4 : G;
-    p.cap = 8;
-    p.scale_log2 = softmax_scale * 1.4426950408889634f;
-    p.ws = ws;
-    p.dev_status = dev_status;
-    return launch_decode_attn(p, G, n_kv_heads, 1, s);
-}
-
 }  // namespace mfar

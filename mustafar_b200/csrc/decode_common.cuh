@@ -153,7 +153,7 @@ constexpr int kPartialStride = kD + 4;  // floats; keeps records 16-byte aligned
 constexpr int kPartM = kD;
 constexpr int kPartL = kD + 1;
 
-enum { MODE_ATTN = 0, MODE_KEY = 1, MODE_VALUE = 2 };
+enum { MODE_KEY = 1, MODE_VALUE = 2 };
 constexpr int kSlackHalves = 64;  // a decode never reads further than this past a stage's values
 constexpr int kMaxBlocksPerSplit = 256;
 
@@ -242,13 +242,6 @@ int launch_decode_attn_quant(const DecodeParams& p, int G, int bits, bool group3
 // merge of the split-KV records (normalise = 1) or plain sum (normalise = 0), one CTA per q head
 int launch_combine(const float* ws, int nrec, int G, int normalise, void* out, int64_t out_stride, int n_q_heads,
                    cudaStream_t s);
-// dense recent-token window as split record `rec_index` of a workspace with rec_index + 1 records per kv head.
-// halves8: with G = 8 the records are laid out as two sets of 4 query heads per kv head
-// ([kv head * 2 + half][record][4]) instead of [kv head][record][8]
-int launch_window_record(const void* q, int64_t q_stride, int n_kv_heads, int G, const void* kwin, const void* vwin,
-                         int64_t win_hs, int64_t win_ts, int W, const int* W_dev, float softmax_scale, float* ws,
-                         int rec_index, unsigned* dev_status, cudaStream_t s, bool halves8 = false);
-
 // Split count of the 64-token-block decode kernels.  The grid is n_kv_heads * ns CTAs of bps = ceil(nblk / ns) blocks.
 // The cost of a candidate follows a model fitted to a measured sweep of ns over batch 1..64 and
 // 4k..32k tokens on a B200 (all times in units of one block on an otherwise idle SM, ~2 us):

@@ -118,7 +118,6 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
     float* qh = reinterpret_cast<float*>(smem + lay.qh);                    // [128][G]
     float* spart = reinterpret_cast<float*>(smem + lay.spart);              // [plane][G][64]
     float* ps = reinterpret_cast<float*>(smem + lay.ps);                    // [64][G]
-    float* alpha_s = reinterpret_cast<float*>(smem + lay.alpha);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     // hq numbers the (kv head, group of G query heads) pairs; with kv_share > 1 several of them read the same kv head
@@ -180,9 +179,6 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
 #pragma unroll
         for (int g = 0; g < G; ++g) acc_o[i][g] = 0.f;
     constexpr int kHeadsPerWarp = (G + kQWarps - 1) / kQWarps;
-    float m_run[kHeadsPerWarp], l_run[kHeadsPerWarp];
-#pragma unroll
-    for (int j = 0; j < kHeadsPerWarp; ++j) { m_run[j] = -INFINITY; l_run[j] = 0.f; }
 
     for (int i = 0; i < nb; ++i) {
         cp_async_wait_all();
@@ -249,21 +245,9 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
                         s0 += t.x;
                         s1 += t.y;
                     }
-                    if (MODE == MODE_KEY) {
-                        *reinterpret_cast<__half2*>(p.s_out + (static_cast<int64_t>(hq) * G + g) * p.s_stride +
-                                                    static_cast<int64_t>(blk0 + i) * 64 + 2 * lane) = __floats2half2_rn(s0, s1);
-                    } else {
-                        s0 *= p.scale_log2;
-                        s1 *= p.scale_log2;
-                        const float m_new = fmaxf(m_run[j], warp_max_f32(fmaxf(s0, s1)));
-                        const float a = fast_exp2(m_run[j] - m_new);
-                        const float p0 = fast_exp2(s0 - m_new), p1 = fast_exp2(s1 - m_new);
-                        l_run[j] = l_run[j] * a + (p0 + p1);
-                        m_run[j] = m_new;
-                        ps[(2 * lane) * G + g] = p0;
-                        ps[(2 * lane + 1) * G + g] = p1;
-                        if (lane == 0) alpha_s[g] = a;
-                    }
+                    // MODE_KEY (the only mode that gets here): the scores leave as they are
+                    *reinterpret_cast<__half2*>(p.s_out + (static_cast<int64_t>(hq) * G + g) * p.s_stride +
+                                                static_cast<int64_t>(blk0 + i) * 64 + 2 * lane) = __floats2half2_rn(s0, s1);
                 }
             }
         }
@@ -271,18 +255,6 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
         __syncthreads();
 
         // ------------------------------------------------------------ V phase
-        if (MODE == MODE_ATTN) {
-            float a[G];
-            bool any = false;
-#pragma unroll
-            for (int g = 0; g < G; ++g) { a[g] = alpha_s[g]; any |= (a[g] != 1.f); }
-            if (any) {
-#pragma unroll
-                for (int t = 0; t < 8; ++t)
-#pragma unroll
-                    for (int g = 0; g < G; ++g) acc_o[t][g] *= a[g];
-            }
-        }
         const int half_id = gi & 1, par = gi >> 1;
 #pragma unroll 8
         for (int s = 0; s < 16 / 2; ++s) {
@@ -319,19 +291,6 @@ __global__ void __launch_bounds__(kQThreads, 4) decode_quant_kernel(QDecodeParam
 #pragma unroll
         for (int w = 0; w < kQWarps; ++w) s += red[(static_cast<size_t>(w) * G + g) * kD + c];
         rec[g * kPartialStride + c] = s;
-    }
-    if (MODE == MODE_ATTN) {
-#pragma unroll
-        for (int j = 0; j < kHeadsPerWarp; ++j) {
-            const int g = warp + j * kQWarps;
-            if (g < G) {
-                const float l = warp_sum_f32(l_run[j]);
-                if (lane == 0) {
-                    rec[g * kPartialStride + kPartM] = m_run[j];
-                    rec[g * kPartialStride + kPartL] = l;
-                }
-            }
-        }
     }
 }
 

@@ -110,7 +110,7 @@ def bench_compress(quick):
     emit("prune only", us, 2 * Bh * L * D * 2, heads=Bh, tokens=L)
 
 
-def bench_compress_fp16(quick):
+def bench_compress_fp16(quick, iters=3, warmup=1):
     """Only the fused prune+compress kernel (K and V, 70 %) and the prune-only kernel: few launches,
     the case to put under a profiler."""
     Bh, L = (16, 4096) if quick else (64, 8192)
@@ -121,11 +121,11 @@ def bench_compress_fp16(quick):
         def run():
             st.tokens = 0
             st.append(x, comp.keep_rank(0.7))
-        us = timed(run, iters=3, warmup=1)
+        us = timed(run, iters=iters, warmup=warmup)
         emit(f"prune+compress {name} fp16", us, x.numel() * 2 + store_bytes(st), heads=Bh, tokens=L, sparsity=0.7)
         if kind == comp.KEY:
             y = torch.empty_like(x)
-            us = timed(lambda: comp.prune(x, 0.7, out=y), iters=3, warmup=1)
+            us = timed(lambda: comp.prune(x, 0.7, out=y), iters=iters, warmup=warmup)
             emit("prune only", us, 2 * x.numel() * 2, heads=Bh, tokens=L)
         # the quantised kernel alone: outputs preallocated once, no host sync inside the timed calls
         T, worst = 2 * L, Bh * 2 * L * 4
@@ -142,7 +142,7 @@ def bench_compress_fp16(quick):
                 bufs[0].data_ptr(), T, bufs[1].data_ptr(), bufs[2].data_ptr(), bufs[3].data_ptr(), bufs[4].data_ptr(),
                 bufs[5].data_ptr(), T, 0, packed.data_ptr(), 0, worst, info.data_ptr(), scratch.data_ptr(), need,
                 info.data_ptr() + 4 * Bh, torch.cuda.current_stream().cuda_stream), "mfar_compress_quant")
-        us = timed(runq, iters=3, warmup=1)
+        us = timed(runq, iters=iters, warmup=warmup)
         emit(f"prune+compress {name} 2-bit (kernel only)", us, x.numel() * 2, heads=Bh, tokens=L, sparsity=0.7)
         del st, x
 
