@@ -24,22 +24,35 @@ from .sharding import max_over_ranks
 
 def _check_peer_reduction(peer, dist, dev) -> None:
     """One fused reduction on known data against NCCL's sum of the same partials, before the buffers are trusted with
-    the timed run; raises when the two disagree or a wait ran out.  Leaves the group's step counter one step on."""
+    the timed run; raises ON EVERY RANK when any rank sees a disagreement or a wait that ran out (every rank walks
+    through the same collectives whatever happens locally).  Leaves the group's step counter one step on."""
     from . import ops
     g = torch.Generator(device=dev).manual_seed(4242 + peer.rank)
     part = (torch.randn(peer.rows, peer.hidden, generator=g, device=dev) * 0.1).half()
     x = torch.ones(peer.rows, peer.hidden, dtype=torch.float16, device=dev)
     w = torch.ones(peer.hidden, dtype=torch.float16, device=dev)
-    peer.slot(0).copy_(part)
-    peer.reduce_add_rmsnorm(x, 0, w, 1e-5)
-    peer.end_step()
+    problem = None
+    try:
+        peer.slot(0).copy_(part)
+        peer.reduce_add_rmsnorm(x, 0, w, 1e-5)
+        peer.end_step()
+    except Exception as e:
+        problem = e
     total = part.float()
     dist.all_reduce(total)
     torch.cuda.synchronize()
-    ops.check_device_status(dev)
-    err = float((x.float() - (1.0 + total)).abs().max())
-    if not err < 2e-2:      # fp16 rounding of 1 + sum of `world` partials of size ~0.1
-        raise RuntimeError(f"peer reduction disagrees with NCCL (max abs error {err})")
+    if problem is None:
+        try:
+            ops.check_device_status(dev)
+            err = float((x.float() - (1.0 + total)).abs().max())
+            if not err < 2e-2:      # fp16 rounding of 1 + sum of `world` partials of size ~0.1
+                raise RuntimeError(f"peer reduction disagrees with NCCL (max abs error {err})")
+        except Exception as e:
+            problem = e
+    bad = torch.tensor([0.0 if problem is None else 1.0], device=dev)
+    dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+    if float(bad) != 0.0:
+        raise RuntimeError(f"peer reduction self-check failed ({problem or 'on another rank'})")
 
 
 def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 4096, new: int = 256,

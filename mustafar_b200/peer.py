@@ -61,19 +61,45 @@ class PeerGroup:
         self._base = C.c_void_p()
         handle = C.create_string_buffer(64)
         self._mapped: list[int] = []
+        # every rank goes through the same collectives whatever fails locally, then all raise together: a rank that
+        # left early would pair its next collective with the others' barrier
+        failure = None
         with torch.cuda.device(self.dev):
-            _lib.check(L.mfar_peer_alloc(nbytes, C.byref(self._base), handle), "mfar_peer_alloc")
+            try:
+                _lib.check(L.mfar_peer_alloc(nbytes, C.byref(self._base), handle), "mfar_peer_alloc")
+                mine = handle.raw
+            except Exception as e:
+                failure, mine = e, None
             gathered = [None] * world
-            dist.all_gather_object(gathered, handle.raw)
+            dist.all_gather_object(gathered, mine)
             bases = []
+            if failure is None and any(g is None for g in gathered):
+                failure = RuntimeError("a peer rank could not allocate its buffers")
             for r in range(world):
+                if failure is not None:
+                    break
                 if r == rank:
                     bases.append(self._base.value)
                     continue
                 ptr = C.c_void_p()
-                _lib.check(L.mfar_peer_open(C.create_string_buffer(gathered[r], 64), C.byref(ptr)), f"mfar_peer_open(rank {r})")
+                try:
+                    _lib.check(L.mfar_peer_open(C.create_string_buffer(gathered[r], 64), C.byref(ptr)), f"mfar_peer_open(rank {r})")
+                except Exception as e:
+                    failure = e
+                    break
                 self._mapped.append(ptr.value)
                 bases.append(ptr.value)
+            everybody = torch.tensor([0.0 if failure is not None else 1.0], device=self.dev)
+            dist.all_reduce(everybody, op=dist.ReduceOp.MIN)
+            if float(everybody) == 0.0:
+                for ptr in self._mapped:
+                    L.mfar_peer_close(ptr)
+                self._mapped = []
+                dist.barrier()          # nobody frees while a peer may still hold a mapping
+                if self._base.value:
+                    L.mfar_peer_free(self._base)
+                self._base = None
+                raise RuntimeError(f"peer buffers could not be set up on every rank ({failure or 'another rank failed'})")
         base = self._base.value
         self.flags = torch.as_tensor(_DeviceView(base, (MAX_PEERS,), "<i4"), device=self.dev)
         self.partials = torch.as_tensor(_DeviceView(base + _FLAG_BYTES, (2, rows, hidden), "<f2"), device=self.dev)
