@@ -335,6 +335,19 @@ int mfar_peer_reduce_add_rmsnorm_f16(void* x, const void* const* partials, void*
                                      const void* weight, void* out, int64_t rows, int hidden, float eps,
                                      int64_t wait_ns, uint32_t* dev_status, void* stream);
 
+/* Arg-max over a vocabulary split across the ranks (vocabulary-parallel lm_head of the tensor-parallel step; no
+ * counterpart in the reference): logits [rows, n_local] fp16 are this rank's slice, columns vocab_offset.. of the whole
+ * vocabulary; n_local a multiple of 8, rows 16-byte aligned.  Two launches: the row-wise local arg-max into
+ * pairs[rank] (8 bytes per row: float value, int32 global index), then the exchange - announce, bounded wait on the
+ * flags (same flag arrays and epoch rule as mfar_peer_reduce_add_rmsnorm_f16, of whose calls this one takes a `call`
+ * index of its own), read all ranks' pairs - which writes tokens[rows] (int64): the largest value, the smallest index
+ * among equal values, identical on every rank.  pairs[world]: HOST array of device pointers, one pair buffer per rank
+ * as mapped into this process.  A wait that runs out sets MFAR_DEV_TIMEOUT and leaves tokens untouched. */
+int mfar_peer_argmax_f16(const void* logits, int64_t row_stride, int64_t rows, int n_local, int vocab_offset,
+                         void* const* pairs, void* const* flags, int world, int rank, const int32_t* step_dev,
+                         int step, int calls_per_step, int call, int64_t* tokens, int64_t wait_ns,
+                         uint32_t* dev_status, void* stream);
+
 /* Set-up of the buffers mfar_peer_reduce_add_rmsnorm_f16 reads across GPUs (one-off, not on the hot path).
  * mfar_peer_alloc: cudaMalloc of `bytes` zeroed bytes on the current device, *ptr = the allocation, handle64 (64 host
  *                  bytes) = its CUDA IPC handle, to be sent to the other ranks' processes by any host channel.

@@ -57,6 +57,7 @@ SIGNATURES = {
     "mfar_add_rmsnorm_f16": (_i32, [_vp, _vp, _vp, _vp, _i64, _i32, _f32, _vp]),
     "mfar_rope_append_f16": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _i64, _i64, _i32, _i32,
                                     _i32, _vp, _vp]),
+    "mfar_peer_argmax_f16": (_i32, [_vp, _i64, _i64, _i32, _i32, _vp, _vp, _i32, _i32, _vp, _i32, _i32, _i32, _vp, _i64, _vp, _vp]),
     "mfar_peer_alloc": (_i32, [_i64, C.POINTER(C.c_void_p), C.c_void_p]),
     "mfar_peer_open": (_i32, [C.c_void_p, C.POINTER(C.c_void_p)]),
     "mfar_peer_close": (_i32, [C.c_void_p]),

@@ -145,6 +145,102 @@ __global__ void __launch_bounds__(256) peer_reduce_rmsnorm_kernel(PeerReducePara
     }
 }
 
+// ---- arg-max over a vocabulary that is split across the ranks (each rank holds the logits of its slice).
+// Two launches: row_argmax_kernel leaves (value, global index) of every row's best local logit in this rank's
+// peer-visible pair buffer; peer_argmax_exchange_kernel then announces, waits (bounded, like the reduction above),
+// reads every rank's pairs through the peer pointers and keeps the best: the largest value, the smallest index among
+// equals, so every rank ends up with the same token.
+struct ArgPair { float v; int idx; };
+
+__global__ void __launch_bounds__(256) row_argmax_kernel(const __half* logits, int64_t stride, int n, int vocab_offset,
+                                                         ArgPair* pairs) {
+    __shared__ float s_v[8];
+    __shared__ int s_i[8];
+    const int tid = threadIdx.x;
+    const __half* row = logits + static_cast<int64_t>(blockIdx.x) * stride;
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int i = tid * 8; i < n; i += 256 * 8) {           // n is a multiple of 8, rows are 16-byte aligned
+        const uint4 q = *reinterpret_cast<const uint4*>(row + i);
+        const __half2* h2 = reinterpret_cast<const __half2*>(&q);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __half22float2(h2[k]);
+            if (f.x > best) { best = f.x; at = i + 2 * k; }        // ascending indices: the first of equals stays
+            if (f.y > best) { best = f.y; at = i + 2 * k + 1; }
+        }
+    }
+#pragma unroll
+    for (int d = 16; d; d >>= 1) {
+        const float ov = __shfl_xor_sync(kFull, best, d);
+        const int oi = __shfl_xor_sync(kFull, at, d);
+        if (ov > best || (ov == best && oi < at)) { best = ov; at = oi; }
+    }
+    if ((tid & 31) == 0) { s_v[tid >> 5] = best; s_i[tid >> 5] = at; }
+    __syncthreads();
+    if (tid == 0) {
+#pragma unroll
+        for (int w = 1; w < 8; ++w)
+            if (s_v[w] > best || (s_v[w] == best && s_i[w] < at)) { best = s_v[w]; at = s_i[w]; }
+        ArgPair r;
+        r.v = best;
+        r.idx = at == 0x7fffffff ? vocab_offset : vocab_offset + at;
+        pairs[blockIdx.x] = r;
+    }
+}
+
+struct ArgExchangeParams {
+    const ArgPair* pairs[kMaxPeers];
+    unsigned* flags[kMaxPeers];
+    int world, rank;
+    const int* step_dev;
+    int step, calls_per_step, call, rows;
+    long long* tokens;
+    unsigned long long wait_ns;
+    unsigned* dev_status;
+};
+
+__global__ void __launch_bounds__(256) peer_argmax_exchange_kernel(ArgExchangeParams p) {
+    __shared__ int s_ok;
+    const int tid = threadIdx.x;
+    const int step = p.step_dev ? *p.step_dev : p.step;
+    const unsigned epoch = static_cast<unsigned>(step) * static_cast<unsigned>(p.calls_per_step) + static_cast<unsigned>(p.call) + 1u;
+    if (tid < p.world) {          // this rank's pairs were written by the launch before this one
+        __threadfence_system();
+        st_sys_u32(p.flags[tid] + p.rank, epoch);
+    }
+    if (tid == 0) s_ok = 1;
+    __syncthreads();
+    if (tid < p.world) {
+        const unsigned* f = p.flags[p.rank] + tid;
+        const unsigned long long t0 = global_timer_ns();
+        const bool broken = p.dev_status && (ld_volatile_u32(p.dev_status) & MFAR_DEV_TIMEOUT);
+        bool ok = !(broken && static_cast<int>(ld_sys_u32(f) - epoch) < 0);
+        unsigned spins = 0;
+        while (ok && static_cast<int>(ld_sys_u32(f) - epoch) < 0) {
+            if ((++spins & 63u) == 0 && global_timer_ns() - t0 > p.wait_ns) ok = false;
+        }
+        if (!ok) s_ok = 0;
+    }
+    __syncthreads();
+    if (!s_ok) {
+        if (tid == 0 && p.dev_status) atomicOr(p.dev_status, MFAR_DEV_TIMEOUT);
+        return;
+    }
+    for (int row = tid; row < p.rows; row += 256) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int r = 0; r < p.world; ++r) {
+            unsigned long long raw;
+            asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(raw) : "l"(p.pairs[r] + row) : "memory");
+            const float v = __uint_as_float(static_cast<unsigned>(raw));
+            const int idx = static_cast<int>(raw >> 32);
+            if (v > best || (v == best && idx < at) || at == 0x7fffffff) { best = v; at = idx; }
+        }
+        p.tokens[row] = at;
+    }
+}
+
 }  // namespace mfar
 
 using namespace mfar;
@@ -230,5 +326,43 @@ extern "C" int mfar_peer_reduce_add_rmsnorm_f16(void* x, const void* const* part
     p.wait_ns = static_cast<unsigned long long>(wait_ns);
     p.dev_status = dev_status;
     peer_reduce_rmsnorm_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return launch_status();
+}
+
+extern "C" int mfar_peer_argmax_f16(const void* logits, int64_t row_stride, int64_t rows, int n_local, int vocab_offset,
+                                    void* const* pairs, void* const* flags, int world, int rank,
+                                    const int32_t* step_dev, int step, int calls_per_step, int call, int64_t* tokens,
+                                    int64_t wait_ns, uint32_t* dev_status, void* stream) {
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || rows < 0 || n_local <= 0 || (n_local % 8) ||
+        vocab_offset < 0 || calls_per_step <= 0 || call < 0 || call >= calls_per_step || step < 0 || wait_ns <= 0)
+        return MFAR_ERR_ARG;
+    if (rows == 0) return MFAR_OK;
+    if (!logits || !pairs || !flags || !tokens) return MFAR_ERR_ARG;
+    if (rows > 65535) return MFAR_ERR_LIMIT;
+    if ((reinterpret_cast<uintptr_t>(logits) & 15) || (row_stride & 7)) return MFAR_ERR_ALIGN;
+    ArgExchangeParams p{};
+    for (int r = 0; r < world; ++r) {
+        if (!pairs[r] || !flags[r]) return MFAR_ERR_ARG;
+        if ((reinterpret_cast<uintptr_t>(pairs[r]) & 7) || (reinterpret_cast<uintptr_t>(flags[r]) & 3)) return MFAR_ERR_ALIGN;
+        p.pairs[r] = static_cast<const ArgPair*>(pairs[r]);
+        p.flags[r] = static_cast<unsigned*>(flags[r]);
+    }
+    p.world = world;
+    p.rank = rank;
+    p.step_dev = step_dev;
+    p.step = step;
+    p.calls_per_step = calls_per_step;
+    p.call = call;
+    p.rows = static_cast<int>(rows);
+    p.tokens = reinterpret_cast<long long*>(tokens);
+    p.wait_ns = static_cast<unsigned long long>(wait_ns);
+    p.dev_status = dev_status;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    row_argmax_kernel<<<static_cast<unsigned>(rows), 256, 0, s>>>(static_cast<const __half*>(logits), row_stride, n_local,
+                                                                 vocab_offset,
+                                                                 const_cast<ArgPair*>(p.pairs[rank]));
+    const int st = launch_status();
+    if (st != MFAR_OK) return st;
+    peer_argmax_exchange_kernel<<<1, 256, 0, s>>>(p);
     return launch_status();
 }

@@ -57,11 +57,13 @@ def _check_peer_reduction(peer, dist, dev) -> None:
 
 def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 4096, new: int = 256,
             parallel: str = "dp", sparsity: float = 0.7, layers: int = 32, graph: bool = True, dense: bool = False,
-            bits: int = 16, prune_mode: str = "block", tp_reduce: str = "fused") -> dict:
+            bits: int = 16, prune_mode: str = "block", tp_reduce: str = "fused", lm_head: str = "parallel") -> dict:
     """One generation (prefill + ``new`` greedy steps) on this rank's GPU; returns the result record (the same on
     every rank: times are the maximum over ranks).  ``dist``: an initialised torch.distributed module or None.
     ``tp_reduce``: "fused" = peer-buffer reduction fused with the RMSNorm, whole step one CUDA graph; "nccl" = NCCL
-    all-reduces between graphs (also what "fused" falls back to when the peer mapping cannot be set up)."""
+    all-reduces between graphs (also what "fused" falls back to when the peer mapping cannot be set up).
+    ``lm_head``: "parallel" = with the fused reduction every rank keeps its slice of the vocabulary and the next token
+    comes out of the peer arg-max exchange; "replicated" = every rank computes all logits."""
     tp = world if parallel == "tp" else 1
     shape = LlamaShape(n_layers=layers)
     kw = dict(sparsity=sparsity, seed=1234, tp_rank=rank if tp > 1 else 0, tp_world=tp, dist=dist, sparse=not dense,
@@ -73,7 +75,8 @@ def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 409
         model = None
         if tp_reduce == "fused" and not dense:
             try:
-                model = SparseLlama(shape, batch, prompt + new, dev, tp_fused=True, **kw)
+                model = SparseLlama(shape, batch, prompt + new, dev, tp_fused=True,
+                                    lm_head_parallel=(lm_head == "parallel"), **kw)
                 _check_peer_reduction(model.peer, dist, dev)
                 ok += 1
             except Exception as e:      # e.g. CUDA IPC not permitted between the ranks' containers
@@ -102,11 +105,11 @@ def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 409
     sync()
     e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
     e[0].record()
-    nxt = model.prefill(toks).argmax(-1)
+    nxt = model.prefill_next(toks)
     e[1].record()
     marks = []
     for _ in range(new - 1):
-        nxt = model.decode_step(nxt, graph=graph).argmax(-1)
+        nxt = model.decode_next(nxt, graph=graph)
         marks.append(torch.cuda.Event(enable_timing=True))
         marks[-1].record()
     e[2].record()
@@ -129,6 +132,7 @@ def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 409
     decode_ms = max_over_ranks(e[1].elapsed_time(e[2]), dist, dev)
     compress_ms = max_over_ranks(model.prefill_compress_ms, dist, dev)
     seqs = batch * (1 if tp > 1 else world)
+    lm_head_used = "vocabulary-parallel" if getattr(model, "vocab_parallel", False) else "replicated"
     # bytes the compressed part of the cache takes per (token, kv head), K + V, measured on the first layer of this rank
     cache_bytes = None
     if not dense and model.compressed:
@@ -154,6 +158,7 @@ def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 409
                                f"batch {batch} per {'job' if tp > 1 else 'GPU'}, sparsity {sparsity}, window 128, "
                                f"pruning per {prune_mode}",
                    "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}", "partial_sum_reduction": reduce_used,
+                   "lm_head": lm_head_used,
                    "cache": "dense-pruned torch" if dense else ("sparse fp16" if bits == 16 else f"sparse {bits}-bit"),
                    "cuda_graph": (False if (not graph or dense) else
                                   ("one graph per stretch between collectives" if reduce_used == "nccl" else True))},
@@ -174,6 +179,8 @@ def main():
                     help="16: pruned values kept as fp16; 4 / 2: quantised per tile")
     ap.add_argument("--tp-reduce", default="fused", choices=["fused", "nccl"],
                     help="tensor parallel only: partial sums through the fused peer-buffer kernel or through NCCL")
+    ap.add_argument("--lm-head", default="parallel", choices=["parallel", "replicated"],
+                    help="tensor parallel with the fused reduction only: split the lm_head over the vocabulary")
     ap.add_argument("--prune-mode", default="block", choices=["block", "step"],
                     help="block: prune with the compression, 256 tokens at a time; step: prune the token that leaves "
                          "the residual window at every decode step")
@@ -187,7 +194,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     res = run_e2e(dev, rank, world, dist, a.batch, a.prompt, a.new, a.parallel, a.sparsity, a.layers, not a.no_graph,
-                  a.dense, a.bits, a.prune_mode, a.tp_reduce)
+                  a.dense, a.bits, a.prune_mode, a.tp_reduce, a.lm_head)
     if rank == 0:
         print(json.dumps(res))
     if dist is not None:

@@ -76,7 +76,8 @@ class SparseLlama:
 
     def __init__(self, shape: LlamaShape, batch: int, max_tokens: int, device, sparsity: float = 0.7,
                  residual: int = 128, seed: int = 0, tp_rank: int = 0, tp_world: int = 1, dist=None,
-                 sparse: bool = True, cache_bits: int = 16, prune_mode: str = "block", tp_fused: bool = False):
+                 sparse: bool = True, cache_bits: int = 16, prune_mode: str = "block", tp_fused: bool = False,
+                 lm_head_parallel: bool = False):
         assert shape.n_kv_heads % tp_world == 0 and shape.ffn % tp_world == 0
         self.s, self.B, self.dev = shape, batch, torch.device(device)
         self.sparsity, self.residual, self.sparse = sparsity, residual, sparse
@@ -105,6 +106,17 @@ class SparseLlama:
         q0, k0 = tp_rank * self.hq * D, tp_rank * self.hkv * D
         self.embed = rnd(shape.vocab, hd)
         self.lm_head = rnd(shape.vocab, hd)
+        # vocabulary-parallel lm_head (only with the peer buffers, whose arg-max exchange picks the token): this rank
+        # keeps the rows of its slice of the vocabulary; logits are then local and `decode_next` returns the ids
+        self.vocab_parallel = bool(lm_head_parallel and tp_fused and tp_world > 1 and sparse)
+        self.v0 = 0
+        if self.vocab_parallel:
+            vl = shape.vocab // tp_world
+            if shape.vocab % tp_world or vl % 8:
+                raise RuntimeError("vocabulary-parallel lm_head needs vocab / ranks to be a multiple of 8")
+            self.v0 = tp_rank * vl
+            self.lm_head = self.lm_head[self.v0:self.v0 + vl].contiguous()
+            self._tok_out = torch.empty(batch, dtype=torch.int64, device=self.dev)
         self.norm = torch.ones(hd, dtype=torch.float16, device=self.dev)
         self.layers = []
         Bh = batch * self.hkv
@@ -152,7 +164,8 @@ class SparseLlama:
         self.peer = None
         if tp_world > 1 and tp_fused and sparse:
             from .peer import PeerGroup
-            self.peer = PeerGroup(dist, tp_rank, tp_world, self.dev, batch, shape.hidden, 2 * shape.n_layers)
+            self.peer = PeerGroup(dist, tp_rank, tp_world, self.dev, batch, shape.hidden, 2 * shape.n_layers,
+                                  argmax_call=self.vocab_parallel)
         self._decode_ws = None
         if self.sparse:
             _, nbytes = ops.plan(batch * self.hkv, self.max_tokens, self.wcap, self.G)
@@ -354,6 +367,8 @@ class SparseLlama:
         if dev_state:
             self._state += self._state_step
         self._step_out = F.linear(add_norm(delta, self.norm), self.lm_head)
+        if self.vocab_parallel:
+            self._step_tok = peer.argmax(self._step_out, self.v0, out=self._tok_out)
         if peer is not None:
             peer.end_step()
 
@@ -462,11 +477,29 @@ class SparseLlama:
         self._stage_hint = None
 
     @torch.no_grad()
+    @torch.no_grad()
+    def prefill_next(self, tokens: torch.Tensor) -> torch.Tensor:
+        """prefill, then the greedy choice for the next position [B] (with a vocabulary-parallel lm_head the ranks'
+        local logits meet in the peer arg-max exchange; otherwise a plain arg-max)."""
+        logits = self.prefill(tokens)
+        if not self.vocab_parallel:
+            return logits.argmax(-1)
+        self._logits_last = logits = logits.contiguous()
+        tok = self.peer.argmax(logits, self.v0).clone()
+        self.peer.end_step()
+        return tok
+
+    @torch.no_grad()
+    def decode_next(self, token: torch.Tensor, graph: bool = False) -> torch.Tensor:
+        """One decode step and the greedy choice for the position after it [B] (see prefill_next)."""
+        logits = self.decode_step(token, graph)
+        return self._step_tok.clone() if self.vocab_parallel else logits.argmax(-1)
+
     def generate(self, tokens: torch.Tensor, steps: int, graph: bool = False):
         """Greedy decoding; returns the generated ids [B, steps]."""
-        nxt = self.prefill(tokens).argmax(-1)
+        nxt = self.prefill_next(tokens)
         out = [nxt]
         for _ in range(steps - 1):
-            nxt = self.decode_step(nxt, graph).argmax(-1)
+            nxt = self.decode_next(nxt, graph)
             out.append(nxt)
         return torch.stack(out, dim=1)

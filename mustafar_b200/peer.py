@@ -45,7 +45,9 @@ class _DeviceView:
 
 class PeerGroup:
     def __init__(self, dist, rank: int, world: int, device, rows: int, hidden: int, calls_per_step: int,
-                 wait_ms: float = 2000.0):
+                 wait_ms: float = 2000.0, argmax_call: bool = False):
+        """``calls_per_step`` reductions per step (even), plus one arg-max exchange per step when ``argmax_call``
+        (it takes the call index ``calls_per_step`` and has a buffer of its own)."""
         if world > MAX_PEERS:
             raise RuntimeError(f"at most {MAX_PEERS} ranks")
         if calls_per_step <= 0 or calls_per_step % 2:
@@ -53,11 +55,13 @@ class PeerGroup:
                                "from the last call of a step to the first of the next")
         self.rank, self.world, self.dev = rank, world, torch.device(device)
         self.rows, self.hidden, self.calls_per_step = rows, hidden, calls_per_step
+        self.epoch_calls = calls_per_step + (1 if argmax_call else 0)      # flag epochs consumed per step
         self.wait_ns = int(wait_ms * 1e6)
         self._dist = dist
         L = _lib.lib()
         slot_bytes = rows * hidden * 2
-        nbytes = _FLAG_BYTES + 2 * slot_bytes
+        pair_off = _FLAG_BYTES + 2 * slot_bytes                        # (value, index) per row for the arg-max exchange
+        nbytes = pair_off + 8 * rows
         self._base = C.c_void_p()
         handle = C.create_string_buffer(64)
         self._mapped: list[int] = []
@@ -109,6 +113,7 @@ class PeerGroup:
         dist.barrier()      # every rank has opened every handle before anybody writes
         self._ptr_arrays = {slot: (C.c_void_p * world)(*[b + _FLAG_BYTES + slot * slot_bytes for b in bases]) for slot in (0, 1)}
         self._flag_array = (C.c_void_p * world)(*bases)
+        self._pair_array = (C.c_void_p * world)(*[b + pair_off for b in bases])
 
     def close(self) -> None:
         """Collective: unmaps the peers' blocks, then (after a barrier) frees this rank's own."""
@@ -139,9 +144,28 @@ class PeerGroup:
             out = torch.empty_like(x)
         st = _lib.lib().mfar_peer_reduce_add_rmsnorm_f16(
             x.data_ptr(), self._ptr_arrays[slot_of(call)], self._flag_array, self.world, self.rank, self.step.data_ptr(), 0,
-            self.calls_per_step, call, weight.data_ptr(), out.data_ptr(), self.rows, self.hidden, float(eps),
+            self.epoch_calls, call, weight.data_ptr(), out.data_ptr(), self.rows, self.hidden, float(eps),
             self.wait_ns, _dev_status(x.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
         _lib.check(st, "mfar_peer_reduce_add_rmsnorm_f16")
+        return out
+
+    def argmax(self, logits: torch.Tensor, vocab_offset: int, out: torch.Tensor | None = None) -> torch.Tensor:
+        """logits [rows, n_local] fp16: this rank's slice of the vocabulary, starting at ``vocab_offset`` -> int64 [rows],
+        the index of the largest logit over all ranks' slices (the smallest index among equals), the same on every
+        rank.  Takes the step's last call index; the group must have been built with ``argmax_call=True``."""
+        from .ops import _dev_status
+        if self.epoch_calls == self.calls_per_step:
+            raise RuntimeError("PeerGroup was built without argmax_call=True")
+        if logits.dim() != 2 or logits.shape[0] != self.rows or logits.dtype != torch.float16 or logits.stride(1) != 1 \
+                or logits.shape[1] % 8 or logits.stride(0) % 8 or logits.data_ptr() % 16:
+            raise RuntimeError("argmax: logits must be float16 [rows, n_local], n_local a multiple of 8, rows 16-byte aligned")
+        if out is None:
+            out = torch.empty(self.rows, dtype=torch.int64, device=logits.device)
+        st = _lib.lib().mfar_peer_argmax_f16(
+            logits.data_ptr(), logits.stride(0), self.rows, logits.shape[1], int(vocab_offset), self._pair_array,
+            self._flag_array, self.world, self.rank, self.step.data_ptr(), 0, self.epoch_calls, self.calls_per_step,
+            out.data_ptr(), self.wait_ns, _dev_status(logits.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+        _lib.check(st, "mfar_peer_argmax_f16")
         return out
 
     def end_step(self) -> None:

@@ -107,3 +107,45 @@ def test_peer_block_allocates_zeroed_and_is_viewable_by_torch():
     assert lib.mfar_peer_free(base) == 0
     assert lib.mfar_peer_alloc(0, C.byref(base), handle) == 1          # MFAR_ERR_ARG
     assert lib.mfar_peer_close(None) == 0 and lib.mfar_peer_free(None) == 0
+
+
+def test_split_vocabulary_argmax_picks_the_global_best_and_the_lowest_index_of_equals():
+    """mfar_peer_argmax_f16 as rank 0 of two on one GPU: the "peer" pair buffer is filled by hand and its flag is set
+    beforehand.  Rows exercise: best in the local slice, best in the peer's slice, a tie across slices (the lower
+    index wins), a tie inside the local slice."""
+    from mustafar_b200 import _lib
+    lib = _lib.lib()
+    rows, n_local, off = 4, 1024, 0
+    g = torch.Generator(device="cuda").manual_seed(11)
+    logits = torch.randn(rows, n_local, generator=g, device="cuda").half().clamp_(-3, 3)
+    logits[0, 700] = 9.0                                   # local best
+    logits[1, 5] = 4.0                                     # the peer has 6.0 for this row
+    logits[2, 900] = 7.0                                   # tie with the peer's 7.0: index 900 < 1024 + 3
+    logits[3, 10] = 8.0
+    logits[3, 400] = 8.0                                   # tie inside the slice: 10 wins
+    pairs = [torch.zeros(rows, 2, dtype=torch.int32, device="cuda") for _ in range(2)]
+    peer_vals = torch.tensor([1.0, 6.0, 7.0, -1.0], dtype=torch.float32)
+    pairs[1][:, 0] = peer_vals.view(torch.int32).cuda()
+    pairs[1][:, 1] = torch.tensor([1024 + 1, 1024 + 2, 1024 + 3, 1024 + 4], dtype=torch.int32).cuda()
+    flags = [torch.zeros(8, dtype=torch.int32, device="cuda") for _ in range(2)]
+    flags[0][1] = 5                                        # epoch of (step 0, call 4 of 5)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tokens = torch.full((rows,), -1, dtype=torch.int64, device="cuda")
+    pa = (C.c_void_p * 2)(pairs[0].data_ptr(), pairs[1].data_ptr())
+    fa = (C.c_void_p * 2)(flags[0].data_ptr(), flags[1].data_ptr())
+    st = lib.mfar_peer_argmax_f16(logits.data_ptr(), logits.stride(0), rows, n_local, off, pa, fa, 2, 0, None, 0, 5, 4,
+                                  tokens.data_ptr(), int(1e9), status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    assert tokens.tolist() == [700, 1024 + 2, 900, 10]
+    assert int(flags[1][0]) == 5                           # announced to the "peer"
+    # local pairs are what a peer would read
+    assert pairs[0][:, 1].tolist() == [700, 5, 900, 10]
+    # the peer never announces the next epoch: bounded wait, tokens untouched
+    tokens.fill_(-1)
+    st = lib.mfar_peer_argmax_f16(logits.data_ptr(), logits.stride(0), rows, n_local, off, pa, fa, 2, 0, None, 1, 5, 4,
+                                  tokens.data_ptr(), int(30e6), status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert int(status) & _lib.DEV_TIMEOUT and tokens.tolist() == [-1] * rows

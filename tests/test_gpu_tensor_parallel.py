@@ -25,6 +25,19 @@ def test_tp2_matches_single_gpu(graph, fused):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("graph", ["0", "1"])
+def test_tp2_vocabulary_parallel_lm_head(graph):
+    """Every rank keeps half of the lm_head; the gathered logits match the single-GPU model and the token the peer
+    arg-max exchange picks is a maximum of them, the same on both ranks."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_WORKER_GRAPH=graph, TP_WORKER_FUSED="1", TP_WORKER_LMHEAD="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", "29662", os.path.join(HERE, "tp_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
+    assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
+    assert "TP_WORST_REL_L2" in r.stdout
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_peer_wait_runs_out_when_a_rank_stays_silent():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",

@@ -15,11 +15,39 @@ def main():
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     shape, B, prompt = tiny_shape(), 2, 256 + 128 + 100
+    if os.environ.get("TP_WORKER_LMHEAD", "0") == "1":
+        shape.vocab = 1024          # a slice per rank that is a multiple of 8 logits
     toks = torch.randint(0, shape.vocab, (B, prompt), device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
     fused = os.environ.get("TP_WORKER_FUSED", "0") == "1"   # peer-buffer reduction fused with the RMSNorm instead of NCCL
-    tp = SparseLlama(shape, B, 1024, "cuda", seed=11, tp_rank=rank, tp_world=world, dist=dist, tp_fused=fused)
-    assert (tp.peer is not None) == fused
-    lt = tp.prefill(toks)
+    split_vocab = os.environ.get("TP_WORKER_LMHEAD", "0") == "1"   # vocabulary-parallel lm_head + peer arg-max exchange
+    tp = SparseLlama(shape, B, 1024, "cuda", seed=11, tp_rank=rank, tp_world=world, dist=dist, tp_fused=fused,
+                     lm_head_parallel=split_vocab)
+    assert (tp.peer is not None) == fused and tp.vocab_parallel == (split_vocab and fused)
+
+    def full_logits(local):
+        """all ranks' slices side by side (NCCL, outside any graph): what a replicated lm_head would have produced"""
+        if not tp.vocab_parallel:
+            return local
+        parts = [torch.empty_like(local) for _ in range(world)]
+        dist.all_gather(parts, local.contiguous())
+        return torch.cat(parts, dim=-1)
+
+    def check_token(tok, logits):
+        """the exchanged arg-max is a maximum of the gathered logits, and every rank holds the same ids"""
+        if not tp.vocab_parallel:
+            return
+        picked = logits.gather(1, tok.view(-1, 1)).squeeze(1)
+        assert torch.equal(picked, logits.max(dim=-1).values), (tok, logits.argmax(-1))
+        same = tok.clone()
+        dist.broadcast(same, 0)
+        assert torch.equal(same, tok)
+
+    if tp.vocab_parallel:
+        tok0 = tp.prefill_next(toks)
+        lt = full_logits(tp._logits_last)
+        check_token(tok0, lt)
+    else:
+        lt = tp.prefill(toks)
     ref = SparseLlama(shape, B, 1024, "cuda", seed=11) if rank == 0 else None
     lr = ref.prefill(toks) if rank == 0 else None
     worst = 0.0
@@ -28,7 +56,12 @@ def main():
         nxt = lt.argmax(-1)
         dist.broadcast(nxt, 0)
         # graph: one CUDA graph per stretch between two collectives, the all-reduces launched eagerly in between
-        lt = tp.decode_step(nxt, graph=use_graph)
+        if tp.vocab_parallel:
+            tok = tp.decode_next(nxt, graph=use_graph)
+            lt = full_logits(tp._step_out)
+            check_token(tok, lt)
+        else:
+            lt = tp.decode_step(nxt, graph=use_graph)
         if rank == 0:
             lr = ref.decode_step(nxt)
             err = float(torch.linalg.norm(lt.float() - lr.float()) / torch.linalg.norm(lr.float()))
