@@ -83,10 +83,11 @@ __device__ __forceinline__ void expand_pair(uint4 bm, const unsigned short* va, 
     pb[1] = pb[0] + __popc(bb & 0xf0u);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        unsigned lo = 0, hi = 0;
-        if (ba & (0x80u >> i)) { lo = *pa[i / 4]; ++pa[i / 4]; }
-        if (bb & (0x80u >> i)) { hi = *pb[i / 4]; ++pb[i / 4]; }
-        r[i] = __byte_perm(lo, hi, 0x5410);
+        // one zero per register: tile A's half is loaded straight into it, tile B's half is merged in only when present
+        unsigned v = 0;
+        if (ba & (0x80u >> i)) { v = *pa[i / 4]; ++pa[i / 4]; }
+        if (bb & (0x80u >> i)) { const unsigned hi = *pb[i / 4]; ++pb[i / 4]; v = __byte_perm(v, hi, 0x5410); }
+        r[i] = v;
     }
 }
 
