@@ -119,6 +119,12 @@ class SparseStore:
         """Synchronises and raises if a kernel reported a device-side error."""
         _lib.check_dev_status(int(self.stats[0].item()), "SparseStore")
 
+    def reset(self) -> None:
+        """Forgets the stored tokens (the arena stays allocated): the next append starts at token 0."""
+        self.tokens = 0
+        self.stats.zero_()
+        self._stage_hint = None
+
     def stage_hint(self) -> int:
         """Largest packed size (halves) of any block written so far; synchronises once per append."""
         if self._stage_hint is None:

@@ -106,6 +106,12 @@ class QuantStore:
         """Synchronises and raises if a kernel reported a device-side error (e.g. the code arena is full)."""
         _lib.check_dev_status(int(self.stats[0].item()), "QuantStore")
 
+    def reset(self) -> None:
+        """Forgets the stored tokens (the arena stays allocated): the next append starts at token 0."""
+        self.tokens = 0
+        self.stats.zero_()
+        self.head_tail.zero_()
+
     def as_dict(self) -> dict:
         """The arrays in the shape ``ops_quant.decode_attention_quant`` takes (no copies)."""
         return dict(bitmaps=self.bitmaps, tile_offsets=self.tile_offsets, packed=self.packed.view(-1), counts=self.counts,

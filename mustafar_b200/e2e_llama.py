@@ -57,7 +57,7 @@ def _check_peer_reduction(peer, dist, dev) -> None:
 
 def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 4096, new: int = 256,
             parallel: str = "dp", sparsity: float = 0.7, layers: int = 32, graph: bool = True, dense: bool = False,
-            bits: int = 16, prune_mode: str = "block", tp_reduce: str = "fused", lm_head: str = "parallel") -> dict:
+            bits: int = 16, prune_mode: str = "block", tp_reduce: str = "fused", lm_head: str = "parallel", warm_up: bool = True) -> dict:
     """One generation (prefill + ``new`` greedy steps) on this rank's GPU; returns the result record (the same on
     every rank: times are the maximum over ranks).  ``dist``: an initialised torch.distributed module or None.
     ``tp_reduce``: "fused" = peer-buffer reduction fused with the RMSNorm, whole step one CUDA graph; "nccl" = NCCL
@@ -93,6 +93,8 @@ def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 409
             model = SparseLlama(shape, batch, prompt + new, dev, **kw)
     else:
         model = SparseLlama(shape, batch, prompt + new, dev, **kw)
+    if warm_up:      # what a serving process does at start-up: the step graph is captured before the timed generation
+        model.warm_up(graph)
     g = torch.Generator(device=dev).manual_seed(99 if tp > 1 else 99 + rank)
     toks = torch.randint(0, shape.vocab, (batch, prompt), generator=g, device=dev)
 
@@ -159,6 +161,7 @@ def run_e2e(dev, rank: int, world: int, dist, batch: int = 32, prompt: int = 409
                                f"pruning per {prune_mode}",
                    "parallelism": f"tp{tp}" if tp > 1 else f"dp{world}", "partial_sum_reduction": reduce_used,
                    "lm_head": lm_head_used,
+                   "warm_up": "one short generation first (step graph captured there)" if warm_up else "none",
                    "cache": "dense-pruned torch" if dense else ("sparse fp16" if bits == 16 else f"sparse {bits}-bit"),
                    "cuda_graph": (False if (not graph or dense) else
                                   ("one graph per stretch between collectives" if reduce_used == "nccl" else True))},
@@ -181,6 +184,8 @@ def main():
                     help="tensor parallel only: partial sums through the fused peer-buffer kernel or through NCCL")
     ap.add_argument("--lm-head", default="parallel", choices=["parallel", "replicated"],
                     help="tensor parallel with the fused reduction only: split the lm_head over the vocabulary")
+    ap.add_argument("--no-warm-up", action="store_true",
+                    help="time the first generation of the process (pays library start-up and the graph capture)")
     ap.add_argument("--prune-mode", default="block", choices=["block", "step"],
                     help="block: prune with the compression, 256 tokens at a time; step: prune the token that leaves "
                          "the residual window at every decode step")
@@ -194,7 +199,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
     res = run_e2e(dev, rank, world, dist, a.batch, a.prompt, a.new, a.parallel, a.sparsity, a.layers, not a.no_graph,
-                  a.dense, a.bits, a.prune_mode, a.tp_reduce, a.lm_head)
+                  a.dense, a.bits, a.prune_mode, a.tp_reduce, a.lm_head, not a.no_warm_up)
     if rank == 0:
         print(json.dumps(res))
     if dist is not None:

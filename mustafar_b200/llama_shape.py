@@ -256,6 +256,8 @@ class SparseLlama:
             main.wait_stream(side)
         self.tokens, self.compressed, self.wlen = T, Lc, T - Lc
         self._stage_hint = None
+        if self._graph is not None:     # a step graph captured during an earlier generation: point its counters here
+            self._state.copy_(torch.tensor([self.tokens, self.wlen, self.wlen + 1, self.compressed], dtype=torch.int32))
         out = self._logits(x[:, -1])
         torch.cuda.synchronize(self.dev)
         self.prefill_compress_ms = sum(a.elapsed_time(b) for n, a, b in marks if n == "compress")
@@ -417,7 +419,13 @@ class SparseLlama:
                 for L in self.layers:
                     L.ks.check()
                     L.vs.check()
-                ops.check_device_status()       # e.g. a block larger than the replayed launches stage for
+                ops.check_device_status()
+                # the replayed launches stage `_stage_bound` halves per block; a block with more (tokens with many ties
+                # at the pruning threshold) would only be noticed when it is first decoded, one step later: say so now
+                need = 0 if self.quant else max(max(L.ks.stage_hint(), L.vs.stage_hint()) for L in self.layers)
+                if need > self._stage_bound:
+                    raise RuntimeError(f"a compressed block holds {need} halves, the captured decode launches stage "
+                                       f"{self._stage_bound}: replay would skip it; decode eagerly (graph=False)")
 
     @torch.no_grad()
     def decode_step(self, token: torch.Tensor, graph: bool = False) -> torch.Tensor:
@@ -477,6 +485,28 @@ class SparseLlama:
         self._stage_hint = None
 
     @torch.no_grad()
+    def reset(self) -> None:
+        """Ends a generation: the caches are empty again, allocations and the captured step graph stay, so the next
+        ``prefill`` starts a new generation that replays the same graph."""
+        self.tokens = self.compressed = self.wlen = 0
+        self._stage_hint = None
+        if self.sparse:
+            for L in self.layers:
+                L.ks.reset()
+                L.vs.reset()
+
+    @torch.no_grad()
+    def warm_up(self, graph: bool = True) -> None:
+        """One short throw-away generation (prefill of 448 tokens, a few steps) so that the one-off costs - library
+        initialisation, the first eager step, the capture and instantiation of the step graph - are paid before real
+        traffic, as a serving process does at start-up.  Collective under tensor parallelism."""
+        toks = torch.zeros(self.B, 256 + 128 + 64, dtype=torch.long, device=self.dev)
+        nxt = self.prefill_next(toks)
+        for _ in range(4):
+            nxt = self.decode_next(nxt, graph)
+        torch.cuda.synchronize(self.dev)
+        self.reset()
+
     @torch.no_grad()
     def prefill_next(self, tokens: torch.Tensor) -> torch.Tensor:
         """prefill, then the greedy choice for the next position [B] (with a vocabulary-parallel lm_head the ranks'

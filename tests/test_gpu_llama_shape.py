@@ -111,3 +111,24 @@ def test_quantised_cache_model_matches_dense_model_with_dequantised_cache(bits):
         lq, ld = qm.decode_step(nxt, graph=True).clone(), dm.decode_step(nxt)   # first step eager, then replayed graphs
         assert oracle.rel_l2(lq.float().cpu(), ld.float().cpu()) < 5e-3, i
         nxt = ld.argmax(-1)
+
+
+@pytest.mark.parametrize("bits", [16, 2])
+def test_second_generation_after_reset_replays_the_graph_and_matches_a_fresh_model(bits):
+    """warm_up() runs a throw-away generation (capturing the step graph) and resets; the generation after it must give
+    what a fresh model gives, across a block append, without capturing again."""
+    from mustafar_b200.llama_shape import SparseLlama, tiny_shape
+    shape, B, prompt = tiny_shape(), 2, 256 + 128 + 250
+    toks = torch.randint(0, shape.vocab, (B, prompt), device="cuda", generator=torch.Generator(device="cuda").manual_seed(6))
+    fresh = SparseLlama(shape, B, 1024, "cuda", seed=4, cache_bits=bits)
+    want = fresh.generate(toks, 12, graph=False)
+    m = SparseLlama(shape, B, 1024, "cuda", seed=4, cache_bits=bits)
+    m.warm_up(graph=True)
+    assert m.tokens == 0 and m._graph is not None
+    captured = m._graph
+    got = m.generate(toks, 12, graph=True)
+    assert m._graph is captured
+    assert torch.equal(got, want)
+    assert m.compressed == 512
+    from mustafar_b200 import ops
+    ops.check_device_status()
