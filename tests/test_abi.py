@@ -68,3 +68,30 @@ def test_cpu_tensors_are_refused():
         compression.convert_key_batched(torch.zeros(1, 64, 128, dtype=torch.float16))
     with pytest.raises(RuntimeError):
         compression.prune(torch.zeros(4, 128, dtype=torch.float16), 0.7)
+
+
+def test_header_is_plain_c_and_links_from_c(lib, tmp_path):
+    """The boundary is a C ABI: the header compiles as C99 (no C++ in it) and a C program links against the library
+    and calls entry points that need no GPU - what a cgo / JNI / FFI binding of the reference's host language would do."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "abi.c"
+    src.write_text('#include <stdio.h>\n#include "mustafar_b200.h"\n'
+                   'int main(void) {\n'
+                   '    int ns = 0; size_t bytes = 0;\n'
+                   '    if (mfar_version() < 100) return 1;\n'
+                   '    if (mfar_decode_plan(8, 4096, 128, 0, &ns, &bytes, 4) != MFAR_OK) return 2;\n'
+                   '    if (mfar_prune_fp16(NULL, NULL, 4, 128, 200, NULL) != MFAR_ERR_ARG) return 3;\n'
+                   '    printf("%s %d %zu\\n", mfar_status_string(MFAR_ERR_ALIGN), ns, bytes);\n'
+                   '    return 0;\n}\n')
+    inc = os.path.join(ROOT, "include")
+    libdir = os.path.join(ROOT, "mustafar_b200")
+    exe = tmp_path / "abi"
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", inc, str(src), "-o", str(exe),
+                        "-L", libdir, "-lmustafar_b200", f"-Wl,-rpath,{libdir}"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and "align" in r.stdout, (r.returncode, r.stdout, r.stderr)
