@@ -69,7 +69,7 @@ def other_configs():
     emit, kb.emit = kb.emit, collect
     try:
         kb.bench_compress_fp16(False, iters=10, warmup=3)
-        kb.bench_quant(False, 32, 16384, (2,), (0.7,))
+        kb.bench_quant(False, 32, 16384, (2,), (0.7,), (64,))
         kb.bench_step(False)
     finally:
         kb.emit = emit

@@ -226,20 +226,24 @@ def bench_ops(quick):
     ops.check_device_status()
 
 
-def bench_quant(quick, batch=None, kv_len=None, bit_list=(2, 4), sparsities=(0.5, 0.7)):
+def bench_quant(quick, batch=None, kv_len=None, bit_list=(2, 4), sparsities=(0.5, 0.7), groups=(64, 32)):
+    """Decode over the quantised cache.  group 64 = one scale / zero-point per tile (what the reference implements);
+    group 32 = one per 32 nonzeros of a tile (the variant its write-up describes; oracle restatement only)."""
     B, L = (2, 4096) if quick else (32, 16384)
     B, L = batch or B, kv_len or L
     Bh = B * HKV
     for s in sparsities:
-        for bits in bit_list:
-            kq = cq.compress_quant(synth(Bh, L, 21, True), comp.KEY, comp.keep_rank(s), bits, 64)
-            vq = cq.compress_quant(synth(Bh, L, 22, False), comp.VALUE, comp.keep_rank(s), bits, 64)
+        for bits, group in [(b, g) for g in groups for b in bit_list]:
+            kq = cq.compress_quant(synth(Bh, L, 21, True), comp.KEY, comp.keep_rank(s), bits, group)
+            vq = cq.compress_quant(synth(Bh, L, 22, False), comp.VALUE, comp.keep_rank(s), bits, group)
             kw, vw = synth(Bh, 128, 1, True), synth(Bh, 128, 2, False)
             q = synth(B * HQ, 1, 3, False).view(B * HQ, D)
-            nbytes = sum((8 + 4 + 2 + 2) * d["bitmaps"].numel() + 4 * d["packed"].numel() for d in (kq, vq))
+            nbytes = sum((8 + 4) * d["bitmaps"].numel() + 2 * (d["scales"].numel() + d["zeros"].numel()) +
+                         4 * d["packed"].numel() for d in (kq, vq))
             nbytes += 2 * 2 * Bh * 128 * D + 4 * B * HQ * D
             us = timed(lambda: ops_quant.decode_attention_quant(q, kq, vq, L, kw, vw, G, bits))
-            emit(f"fused decode attention {bits}-bit", us, nbytes, batch=B, kv_len=L, window=128, sparsity=s)
+            emit(f"fused decode attention {bits}-bit" + ("" if group == 64 else ", groups of 32 nonzeros"), us, nbytes,
+                 batch=B, kv_len=L, window=128, sparsity=s)
             del kq, vq
     ops.check_device_status()
 
@@ -285,7 +289,7 @@ def main():
     table = {"compress": bench_compress, "compress_fp16": bench_compress_fp16, "decode_groups": bench_decode_groups, "decode": bench_decode, "ops": bench_ops, "quant": bench_quant, "step": bench_step}
     if a.quant_case:
         b, l, bits, sp = a.quant_case.split(",")
-        bench_quant(False, int(b), int(l), (int(bits),), (float(sp),))
+        bench_quant(False, int(b), int(l), (int(bits),), (float(sp),), (64,))
         return
     for w in a.what.split(","):
         table[w](a.quick)
