@@ -113,7 +113,7 @@ class ClockSampler:
 
     def __exit__(self, *a):
         if self.proc is not None:
-            time.sleep(0.15)
+            time.sleep(0.03)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
@@ -309,12 +309,18 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
-    for _ in range(max(a.warmup, 3)):
-        step()
-    ops.check_device_status(dev)
-    barrier()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(a.steps + 1)]
     with ClockSampler(local) as clocks:
+        for _ in range(max(a.warmup, 3)):
+            step()
+        # nvidia-smi takes a while to deliver its first line (longer with eight of them starting at once) and the
+        # timed region is only tens of milliseconds: keep the GPU under the same load, untimed, until samples arrive
+        t_wait = time.time()
+        while len(clocks.rows) < 2 and time.time() - t_wait < 4.0:
+            step()
+            torch.cuda.synchronize()
+        ops.check_device_status(dev)
+        barrier()
         ev[0].record()
         for i in range(a.steps):
             step()
