@@ -53,8 +53,10 @@ __device__ __forceinline__ unsigned ld_sys_u32(const unsigned* p) {
     return v;
 }
 
-__global__ void __launch_bounds__(256) peer_reduce_rmsnorm_kernel(PeerReduceParams p) {
-    __shared__ float red[8];
+// One CTA per row; hidden / 8 threads (up to 1024), so that with hidden <= 8192 every thread has a single 16-byte piece
+// per rank and all its peer loads are in flight together: one NVLink round trip, not one per piece.
+__global__ void __launch_bounds__(1024) peer_reduce_rmsnorm_kernel(PeerReduceParams p) {
+    __shared__ float red[32];
     __shared__ int s_ok;
     const int tid = threadIdx.x;
     const int step = p.step_dev ? *p.step_dev : p.step;
@@ -90,7 +92,8 @@ __global__ void __launch_bounds__(256) peer_reduce_rmsnorm_kernel(PeerReducePara
     const int64_t row = blockIdx.x;
     __half* xr = p.x + row * p.hidden;
     float ss = 0.f;
-    for (int i = tid * 8; i < p.hidden; i += 256 * 8) {
+    const int nthr = blockDim.x;
+    for (int i = tid * 8; i < p.hidden; i += nthr * 8) {
         float acc[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc[k] = 0.f;
@@ -125,11 +128,10 @@ __global__ void __launch_bounds__(256) peer_reduce_rmsnorm_kernel(PeerReducePara
     if ((tid & 31) == 0) red[tid >> 5] = ss;
     __syncthreads();
     float tot = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) tot += red[i];
+    for (int i = 0; i < (nthr >> 5); ++i) tot += red[i];
     const float scale = rsqrtf(tot / static_cast<float>(p.hidden) + p.eps);
     __half* orow = p.out + row * p.hidden;
-    for (int i = tid * 8; i < p.hidden; i += 256 * 8) {
+    for (int i = tid * 8; i < p.hidden; i += nthr * 8) {
         const uint4 a = *reinterpret_cast<const uint4*>(xr + i);   // own writes: same thread, same addresses
         const uint4 g = *reinterpret_cast<const uint4*>(p.w + i);
         const __half2* ah = reinterpret_cast<const __half2*>(&a);
@@ -325,7 +327,9 @@ extern "C" int mfar_peer_reduce_add_rmsnorm_f16(void* x, const void* const* part
     p.eps = eps;
     p.wait_ns = static_cast<unsigned long long>(wait_ns);
     p.dev_status = dev_status;
-    peer_reduce_rmsnorm_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    const int pieces = hidden / 8;
+    const int threads = pieces >= 1024 ? 1024 : ((pieces + 31) / 32) * 32;
+    peer_reduce_rmsnorm_kernel<<<static_cast<unsigned>(rows), threads, 0, static_cast<cudaStream_t>(stream)>>>(p);
     return launch_status();
 }
 
