@@ -286,6 +286,9 @@ def main():
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
+        # NCCL carries only barriers, scalar reductions and (in the NCCL arm) 256 KiB all-reduces here: in-switch
+        # reduction buys nothing, and without multicast objects a rank that dies cannot disturb its peers' GPUs
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
 
     from mustafar_b200 import ops

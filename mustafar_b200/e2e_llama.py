@@ -197,6 +197,9 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
+        # NCCL carries only barriers, scalar reductions and (in the NCCL arm) 256 KiB all-reduces here: in-switch
+        # reduction buys nothing, and without multicast objects a rank that dies cannot disturb its peers' GPUs
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     res = run_e2e(dev, rank, world, dist, a.batch, a.prompt, a.new, a.parallel, a.sparsity, a.layers, not a.no_graph,
                   a.dense, a.bits, a.prune_mode, a.tp_reduce, a.lm_head, not a.no_warm_up)

@@ -35,6 +35,9 @@ def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # NCCL carries only barriers, scalar reductions and (in the NCCL arm) 256 KiB all-reduces here: in-switch
+    # reduction buys nothing, and without multicast objects a rank that dies cannot disturb its peers' GPUs
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     dist.init_process_group("nccl", device_id=dev)
     group = PeerGroup(dist, rank, world, dev, a.rows, a.hidden, a.calls)
     g = torch.Generator(device=dev).manual_seed(7 + rank)
